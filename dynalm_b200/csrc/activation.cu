@@ -1,6 +1,6 @@
 // Gated activation: out[t, j] = silu(gu[t, j]) * gu[t, inner + j], gu = [gate | up] side by side.
 // silu(x) = x * sigmoid(x) (dynacore/cpu/cpu_device.cpp:117-123; CpuDevice::act_mul :1912-1929).
-// The math is fp32 whatever the storage type.
+// The math is fp32 whatever the storage type. Also here: the squared ReLU of an ungated feed-forward.
 #include "common.cuh"
 
 namespace dl {
@@ -33,7 +33,51 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ ou
   *reinterpret_cast<Vec16*>(out + t * inner + c) = pack<T>(o);
 }
 
+// Squared ReLU: out[i] = max(x[i], 0)^2, the activation of an ungated feed-forward.
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = fmaxf(to_float(x[i]), 0.0f);
+  out[i] = from_float<T>(v * v);
+}
+
+// 16 bytes per access; n counts vectors.
+template <typename T>
+__global__ void relu2_vec_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n) {
+  constexpr int V = PerVec<T>::n;
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float f[V];
+  unpack<T>(reinterpret_cast<const Vec16*>(x)[i], f);
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    f[j] = fmaxf(f[j], 0.0f);
+    f[j] *= f[j];
+  }
+  reinterpret_cast<Vec16*>(out)[i] = pack<T>(f);
+}
+
 }  // namespace dl
+
+// out[i] = max(x[i], 0)^2 over n contiguous elements (out may be x).
+DL_EXPORT int dl_relu2(int dtype, const void* x, void* out, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (dtype != 0 && dtype != 1) return DL_ERR_UNSUPPORTED;
+  const int threads = 256;
+  const int vec = dtype == 0 ? 4 : 8;
+  if (n % vec == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    const size_t nv = static_cast<size_t>(n / vec);
+    const unsigned blocks = static_cast<unsigned>((nv + threads - 1) / threads);
+    if (dtype == 0) dl::relu2_vec_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(x), static_cast<float*>(out), nv);
+    else dl::relu2_vec_kernel<dl::bf16><<<blocks, threads, 0, stream>>>(static_cast<const dl::bf16*>(x), static_cast<dl::bf16*>(out), nv);
+    return dl::launch_status();
+  }
+  const unsigned blocks = static_cast<unsigned>((static_cast<size_t>(n) + threads - 1) / threads);
+  if (dtype == 0) dl::relu2_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(x), static_cast<float*>(out), static_cast<size_t>(n));
+  else dl::relu2_kernel<dl::bf16><<<blocks, threads, 0, stream>>>(static_cast<const dl::bf16*>(x), static_cast<dl::bf16*>(out), static_cast<size_t>(n));
+  return dl::launch_status();
+}
 
 DL_EXPORT int dl_silu_mul(int dtype, const void* gu, void* out, int rows, int inner, cudaStream_t stream) {
   if (rows <= 0 || inner <= 0) return 0;

@@ -50,6 +50,14 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ del
   }
 }
 
+// the same with the element given as an offset from the first part (for deltas addressed without a row pointer)
+template <typename TD>
+__device__ __forceinline__ float delta_at(const TD* d0, int, int parts, size_t part_stride, size_t i) {
+  float d = to_float(d0[i]);
+  for (int p = 1; p < parts; ++p) d += to_float(d0[p * part_stride + i]);
+  return d;
+}
+
 // The same computation with the row held in registers: one pass over global memory, 16-byte
 // accesses, every load of a thread issued before its first use. For widths that are a multiple of 4
 // and at most NV * 1024.
@@ -149,6 +157,52 @@ rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, float de
   }
 }
 
+// One statistic, two norms: the block arrangement that feeds a mixer and a feed-forward from the same stream
+// normalises the same row twice, with two weights. The row is read once:
+//   v = x[src] + (delta_a[src] + delta_b[src])       (either delta optional, each possibly in partial sums)
+//   x[src] = v                                        (when write_residual)
+//   out_a[r] = v * inv * w_a,  out_b[r] = v * inv * w_b (out_b optional),  inv = 1 / sqrt(mean(v^2) + eps)
+// The two deltas may differ in type (a split-K product leaves fp32 partial sums, another product bf16).
+__device__ __forceinline__ float delta_any(const void* p, int dtype, size_t i, int parts, size_t part_stride) {
+  if (p == nullptr) return 0.0f;
+  if (dtype == 0) return delta_at(static_cast<const float*>(p), static_cast<int>(0), parts, part_stride, i);
+  return delta_at(static_cast<const bf16*>(p), static_cast<int>(0), parts, part_stride, i);
+}
+
+template <typename TO>
+__global__ void rmsnorm_pair_kernel(float* __restrict__ x, const void* __restrict__ delta_a, int dtype_a, int parts_a,
+                                    size_t stride_a, const void* __restrict__ delta_b, int dtype_b, int parts_b,
+                                    size_t stride_b, const float* __restrict__ w_a, const float* __restrict__ w_b,
+                                    float eps, TO* __restrict__ out_a, TO* __restrict__ out_b,
+                                    const int* __restrict__ rows, int width, int write_residual) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const size_t src = rows ? static_cast<size_t>(ck_row(rows[r])) : static_cast<size_t>(r);
+  float* xr = x + src * width;
+  const bool any = delta_a != nullptr || delta_b != nullptr;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = xr[i];
+    if (any) {
+      v += delta_any(delta_a, dtype_a, src * width + i, parts_a, stride_a) +
+           delta_any(delta_b, dtype_b, src * width + i, parts_b, stride_b);
+      if (write_residual) xr[i] = v;
+    }
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = xr[i];
+    if (any && !write_residual)
+      v += delta_any(delta_a, dtype_a, src * width + i, parts_a, stride_a) +
+           delta_any(delta_b, dtype_b, src * width + i, parts_b, stride_b);
+    const float n = v * inv;
+    out_a[static_cast<size_t>(r) * width + i] = from_float<TO>(n * w_a[i]);
+    if (out_b != nullptr) out_b[static_cast<size_t>(r) * width + i] = from_float<TO>(n * w_b[i]);
+  }
+}
+
 // x += scale * delta, for a pending residual that no norm follows.
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, float scale, size_t n,
@@ -210,6 +264,28 @@ DL_EXPORT int dl_rmsnorm(int out_dtype, int delta_dtype, float* x, const void* d
   else if (out_dtype == 1 && delta_dtype == 1) DL_LAUNCH(dl::bf16, dl::bf16);
   else if (out_dtype == 1 && delta_dtype == 0) DL_LAUNCH(dl::bf16, float);
   else if (out_dtype == 0 && delta_dtype == 1) DL_LAUNCH(float, dl::bf16);
+  else return DL_ERR_UNSUPPORTED;
+#undef DL_LAUNCH
+  return dl::launch_status();
+}
+
+// The pair norm: see rmsnorm_pair_kernel. dtype codes as above; delta_a, delta_b, rows, w_b and out_b may be null
+// (w_b and out_b together).
+DL_EXPORT int dl_rmsnorm_pair(int out_dtype, float* x, const void* delta_a, int dtype_a, int parts_a,
+                              long long stride_a, const void* delta_b, int dtype_b, int parts_b, long long stride_b,
+                              const float* w_a, const float* w_b, float eps, void* out_a, void* out_b,
+                              const int* rows, int n_rows, int width, int write_residual, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if ((dtype_a != 0 && dtype_a != 1) || (dtype_b != 0 && dtype_b != 1) || (out_b != nullptr && w_b == nullptr))
+    return DL_ERR_UNSUPPORTED;
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+#define DL_LAUNCH(TO)                                                                                               \
+  dl::rmsnorm_pair_kernel<TO><<<n_rows, threads, 0, stream>>>(                                                      \
+      x, delta_a, dtype_a, parts_a, static_cast<size_t>(stride_a), delta_b, dtype_b, parts_b,                       \
+      static_cast<size_t>(stride_b), w_a, w_b, eps, static_cast<TO*>(out_a), static_cast<TO*>(out_b), rows, width,  \
+      write_residual)
+  if (out_dtype == 0) DL_LAUNCH(float);
+  else if (out_dtype == 1) DL_LAUNCH(dl::bf16);
   else return DL_ERR_UNSUPPORTED;
 #undef DL_LAUNCH
   return dl::launch_status();

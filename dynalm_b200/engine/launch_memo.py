@@ -74,15 +74,16 @@ class _Layout:
 
 
 class _Record:
-    __slots__ = ("calls", "own", "library", "pending", "pending_scale")
+    __slots__ = ("calls", "own", "library", "pending", "pending_scale", "pending2")
 
-    def __init__(self, calls, pending, pending_scale):
+    def __init__(self, calls, pending, pending_scale, pending2=None):
         # [(function, arguments, ((argument index, tensor index, offset or None for the tensor itself), ...))]
         self.calls = calls
         self.library = sum(1 for f, _, _ in calls if f is ops.library_mm_again)
         self.own = sum(1 for f, _, _ in calls if ops.counts_as_kernel(f))
         self.pending = pending
         self.pending_scale = pending_scale
+        self.pending2 = pending2
 
 
 def _patches(calls, layout: _Layout):
@@ -131,9 +132,10 @@ class LayerLaunchMemo:
         if not getattr(block, "replay_safe", False):
             return block.forward(stream, ctx, cache, owns_cache)
         layout = self._layout(index, block, cache)
-        pending = stream.pending
+        pending, second = stream.pending, stream.pending2
         key = (self.kinds[index], owns_cache, stream.x.data_ptr(), stream.pending_scale,
-               None if pending is None else (pending.data_ptr(), tuple(pending.shape), pending.dtype), layout.signature)
+               None if pending is None else (pending.data_ptr(), tuple(pending.shape), pending.dtype),
+               None if second is None else (second.data_ptr(), tuple(second.shape), second.dtype), layout.signature)
         if key in self.records:
             record = self.records[key]
             if record is None:
@@ -151,12 +153,13 @@ class LayerLaunchMemo:
             gemm.LIBRARY_CALLS += record.library
             global REPLAYED_LAYERS
             REPLAYED_LAYERS += 1
-            stream.pending, stream.pending_scale = record.pending, record.pending_scale
+            stream.pending, stream.pending_scale, stream.pending2 = record.pending, record.pending_scale, record.pending2
             return stream
         with ops.Recording() as recording:
             stream = block.forward(stream, ctx, cache, owns_cache)
         if any(f is None for f, _ in recording.calls):
             self.records[key] = None             # some work was not written down: this kind runs through its parts
         else:
-            self.records[key] = _Record(_patches(recording.calls, layout), stream.pending, stream.pending_scale)
+            self.records[key] = _Record(_patches(recording.calls, layout), stream.pending, stream.pending_scale,
+                                        stream.pending2)
         return stream

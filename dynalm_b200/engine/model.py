@@ -101,9 +101,18 @@ class Decoder:
         """Final norm and head on the wanted rows only (dynalm/src/model/transformer.cpp:701-718)."""
         n = ctx.num_logit_rows
         normed = self.rt.buffer("final_normed", (n, self.width))
+        self._final_norm(stream, normed, ctx)
+        return self.head.forward(normed, out[:n])
+
+    def _final_norm(self, stream: ResidualStream, normed: torch.Tensor, ctx) -> None:
+        """The final norm of the wanted rows, with what the last block left pending added on the way in."""
+        if stream.pending2 is not None and hasattr(self.final_norm, "forward_pair") and stream.pending_scale == 1.0:
+            self.final_norm.forward_pair(stream.x, normed, None, None, delta_a=stream.pending, delta_b=stream.pending2,
+                                         rows=ctx.logit_rows)
+            return
+        stream.flush_second()
         self.final_norm.forward(stream.x, normed, delta=stream.pending, delta_scale=stream.pending_scale,
                                 rows=ctx.logit_rows)
-        return self.head.forward(normed, out[:n])
 
     def choose(self, stream: ResidualStream, ctx, ids: torch.Tensor, status_to=None) -> bool:
         """The most likely token of every wanted row into `ids`, the logits never leaving the product's kernel; False
@@ -114,8 +123,7 @@ class Decoder:
         normed = self.rt.buffer("final_normed", (n, self.width))
         if not ops.gemm_argmax_applies(normed, self.head.weight):
             return False
-        self.final_norm.forward(stream.x, normed, delta=stream.pending, delta_scale=stream.pending_scale,
-                                rows=ctx.logit_rows)
+        self._final_norm(stream, normed, ctx)
         return self.head.choose(normed, ids, status_to)
 
     def forward(self, ctx, caches, out: Optional[torch.Tensor], choose=None) -> Optional[torch.Tensor]:

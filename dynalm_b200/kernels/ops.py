@@ -26,8 +26,15 @@ _SIGNATURES = {
     "norm": {
         "dl_rmsnorm": [_I, _I, _P, _P, _F, _P, _F, _P, _P, _I, _I, _I, _I, _L, _P, _L, _P],
         "dl_residual_add": [_I, _P, _P, _F, _L, _I, _L, _P],
+        "dl_rmsnorm_pair": [_I, _P, _P, _I, _I, _L, _P, _I, _I, _L, _P, _P, _F, _P, _P, _P, _I, _I, _I, _P],
     },
-    "activation": {"dl_silu_mul": [_I, _P, _P, _I, _I, _P]},
+    "activation": {"dl_silu_mul": [_I, _P, _P, _I, _I, _P], "dl_relu2": [_I, _P, _P, _L, _P]},
+    "qk_norm_cache": {
+        "dl_qk_norm_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _L, _I, _I, _P, _P, _F, _F, _I, _I, _I, _I, _I, _I,
+                                   _I, _I, _P]},
+    "attention_diff": {
+        "dl_diff_attention": [_I, _P, _I, _P, _L, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P,
+                              _F, _F, _P]},
     "rope_cache": {
         "dl_rope_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _I, _I, _P],
         "dl_rope_angles": [_P, _P, _I, _F, _I, _P, _P]},
@@ -433,6 +440,109 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
         raise InvalidArgument("silu_mul: gate_up [rows, 2*inner] and out [rows, inner], contiguous, one dtype")
     _check(_fn("activation", "dl_silu_mul")(dtype_code(out.dtype), _p(gate_up), _p(out), rows, inner, _stream()),
            "silu_mul")
+
+
+def rmsnorm_pair(x: torch.Tensor, weight_a: torch.Tensor, out_a: torch.Tensor, weight_b: Optional[torch.Tensor],
+                 out_b: Optional[torch.Tensor], eps: float, delta_a: Optional[torch.Tensor] = None,
+                 delta_b: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+    """Two norms of one row with one statistic: v = x[src] + (delta_a[src] + delta_b[src]); out_a[r] = rmsnorm(v) *
+    weight_a, out_b[r] = rmsnorm(v) * weight_b (weight_b and out_b may both be None); src = rows[r] or r.
+
+    x: float32 [n, width], updated in place with the sum unless `rows` picks a subset; each delta: [n, width] of either
+    dtype or [parts, n, width] partial sums added in order, the two independently."""
+    _cuda(x, weight_a, out_a, weight_b, out_b, delta_a, delta_b, rows)
+    width = x.shape[1]
+    if x.dtype != torch.float32 or weight_a.dtype != torch.float32 or not x.is_contiguous() or not out_a.is_contiguous() \
+            or out_a.shape[1] != width or weight_a.numel() != width:
+        raise InvalidArgument("rmsnorm_pair: x and weights float32, x and outputs contiguous, widths equal")
+    if (out_b is None) != (weight_b is None) or (out_b is not None and (
+            out_b.shape != out_a.shape or out_b.dtype != out_a.dtype or not out_b.is_contiguous()
+            or weight_b.dtype != torch.float32 or weight_b.numel() != width)):
+        raise InvalidArgument("rmsnorm_pair: the second output and weight come together and match the first")
+    n_rows = out_a.shape[0]
+    if rows is not None:
+        if rows.dtype != torch.int32 or rows.numel() < n_rows:
+            raise InvalidArgument("rmsnorm_pair: rows must be int32 with one entry per output row")
+    elif x.shape[0] < n_rows:
+        raise InvalidArgument("rmsnorm_pair: fewer input rows than output rows")
+    parts_a, stride_a = _delta_parts(delta_a, width, "rmsnorm_pair")
+    parts_b, stride_b = _delta_parts(delta_b, width, "rmsnorm_pair")
+    check_limits("norm", rows=x.shape[0])
+    _take_ahead()
+    _check(_fn("norm", "dl_rmsnorm_pair")(
+        dtype_code(out_a.dtype), _p(x), _p(delta_a), dtype_code(delta_a.dtype) if delta_a is not None else 0, parts_a,
+        stride_a, _p(delta_b), dtype_code(delta_b.dtype) if delta_b is not None else 0, parts_b, stride_b, _p(weight_a),
+        _p(weight_b), eps, _p(out_a), _p(out_b), _p(rows), n_rows, width, 0 if rows is not None else 1, _stream()),
+        "rmsnorm_pair")
+
+
+def relu2(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = max(x, 0)^2 elementwise (out may be x); both contiguous, of one dtype."""
+    _cuda(x, out)
+    if x.shape != out.shape or x.dtype != out.dtype or not x.is_contiguous() or not out.is_contiguous():
+        raise InvalidArgument("relu2: x and out contiguous, of one shape and dtype")
+    _check(_fn("activation", "dl_relu2")(dtype_code(x.dtype), _p(x), _p(out), x.numel(), _stream()), "relu2")
+
+
+def qk_norm_cache_write(qkv: torch.Tensor, positions: torch.Tensor, row_slot: torch.Tensor,
+                        block_table: Optional[torch.Tensor], cache: Optional[torch.Tensor], k_off: int, v_off: int,
+                        q_weight: torch.Tensor, k_weight: Optional[torch.Tensor], eps: float, temp_coef: float,
+                        temp_every: int, n_q_units: int, n_k_units: int, dim: int, v_width: int, page_size: int,
+                        write_cache: bool = True) -> None:
+    """Per-unit RMS norm of the queries of `qkv` in place (with the position-dependent temperature when temp_every >
+    0), and, with write_cache, the normalised keys and the values into each row's record of the paged cache
+    [pages, page_size, record]; see csrc/qk_norm_cache.cu. qkv: [rows, >= (n_q_units + n_k_units) * dim + v_width]."""
+    _cuda(qkv, positions, row_slot, block_table, cache, q_weight, k_weight)
+    _rows_contiguous(qkv, "qkv")
+    rows = qkv.shape[0]
+    need = n_q_units * dim + ((n_k_units * dim + v_width) if write_cache else 0)
+    if qkv.shape[1] < need:
+        raise InvalidArgument("qk_norm_cache_write: qkv is narrower than its units")
+    if q_weight.dtype != torch.float32 or q_weight.numel() != dim:
+        raise InvalidArgument("qk_norm_cache_write: the query norm weight must be float32 [dim]")
+    record = 0
+    if write_cache:
+        if cache is None or block_table is None or k_weight is None:
+            raise InvalidArgument("qk_norm_cache_write: a cache write needs the cache, a block table and the key norm weight")
+        if cache.dtype != qkv.dtype or not cache.is_contiguous() or cache.dim() != 3 or cache.shape[1] != page_size:
+            raise InvalidArgument("qk_norm_cache_write: the cache must be contiguous [pages, page_size, record] of qkv's dtype")
+        record = cache.shape[2]
+        if k_off < 0 or v_off < 0 or k_off + n_k_units * dim > record or v_off + v_width > record:
+            raise InvalidArgument("qk_norm_cache_write: keys or values do not fit the record")
+        if k_weight.dtype != torch.float32 or k_weight.numel() != dim:
+            raise InvalidArgument("qk_norm_cache_write: the key norm weight must be float32 [dim]")
+        if block_table.dtype != torch.int32 or block_table.stride(-1) != 1:
+            raise InvalidArgument("qk_norm_cache_write: block_table must be int32 rows")
+        check_limits("qk_norm_cache", pages=cache.shape[0], requests=block_table.shape[0], rows=rows)
+    max_blocks = block_table.stride(0) if block_table is not None else 0
+    _check(_fn("qk_norm_cache", "dl_qk_norm_cache_write")(
+        dtype_code(qkv.dtype), _p(qkv), qkv.stride(0), _p(positions), _p(row_slot), _p(block_table), max_blocks,
+        _p(cache), record, k_off, v_off, _p(q_weight), _p(k_weight), eps, temp_coef, int(temp_every), rows, n_q_units,
+        n_k_units, dim, v_width, page_size, 1 if write_cache else 0, _stream()), "qk_norm_cache_write")
+
+
+def diff_attention(q: torch.Tensor, cache: torch.Tensor, k_off: int, v_off: int, block_table: torch.Tensor,
+                   positions: torch.Tensor, row_slot: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int,
+                   dim: int, vdim: int, page_size: int, scale: float, softcap: float, lam: torch.Tensor,
+                   out_scale: float, eps: float) -> None:
+    """Differential attention of every row over its request's cached records, the plain kernel; see
+    csrc/attention_diff.cu. q: [rows, >= n_heads * 2 * dim]; out: [rows, >= n_heads * vdim]; cache: [pages, page_size,
+    record]; lam: one float32 on the device."""
+    _cuda(q, cache, block_table, positions, row_slot, out, lam)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    if dim > 256 or vdim > 256 or n_heads % n_kv_heads:
+        raise Unsupported(f"diff attention: dim {dim} / vdim {vdim} (at most 256), heads {n_heads}:{n_kv_heads}")
+    if q.dtype != out.dtype or cache.dtype != q.dtype or lam.dtype != torch.float32:
+        raise InvalidArgument("diff attention: q, out and the cache share one dtype; lambda is float32")
+    if cache.dim() != 3 or cache.shape[1] != page_size or not cache.is_contiguous() \
+            or k_off + n_kv_heads * 2 * dim > cache.shape[2] or v_off + n_kv_heads * vdim > cache.shape[2]:
+        raise InvalidArgument("diff attention: the cache is not [pages, page_size, record] with room for keys and values")
+    check_limits("attention_diff", pages=cache.shape[0], requests=block_table.shape[0], rows=q.shape[0])
+    _check(_fn("attention_diff", "dl_diff_attention")(
+        dtype_code(q.dtype), _p(q), q.stride(0), _p(cache), cache.shape[2], k_off, v_off, _p(block_table),
+        block_table.stride(0), _p(positions), _p(row_slot), _p(out), out.stride(0), q.shape[0], n_heads, n_kv_heads, dim,
+        vdim, page_size, scale, softcap, _p(lam), out_scale, eps, _stream()), "diff_attention")
 
 
 def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, row_request: torch.Tensor,

@@ -1,8 +1,9 @@
 """How a layer arranges its parts around the residual stream.
 
 "pre_norm" (Llama): x += s * mixer(norm1(x)); x += s * ffn(norm2(x)), s the residual scale
-(dynalm/src/model/transformer.cpp:602-697). The residual stream is float32; the sum of a part's
-output into it is fused into the norm that follows, so a block leaves its last output pending.
+(dynalm/src/model/transformer.cpp:602-697). "parallel": x += mixer(norm1(x)) + ffn(norm2(x)), both
+parts fed from the same x. The residual stream is float32; the sum of a part's output into it is
+fused into the norm that follows, so a block leaves its last output (the parallel one: both) pending.
 """
 
 from __future__ import annotations
@@ -18,17 +19,26 @@ from .base import build_part, register_block
 
 @dataclass
 class ResidualStream:
-    """x: float32 [rows, width]. `pending` (compute dtype) times `pending_scale` is still to be added."""
+    """x: float32 [rows, width]. `pending` (compute dtype) times `pending_scale` is still to be added, and so is
+    `pending2` (unscaled), the second output of an arrangement that leaves two."""
 
     x: torch.Tensor
     pending: Optional[torch.Tensor] = None
     pending_scale: float = 1.0
+    pending2: Optional[torch.Tensor] = None
 
     def flush(self) -> torch.Tensor:
         if self.pending is not None:
             ops.residual_add(self.x, self.pending, self.pending_scale)
             self.pending = None
+        self.flush_second()
         return self.x
+
+    def flush_second(self) -> None:
+        """Adds the second pending output now; for a consumer that takes one delta only."""
+        if self.pending2 is not None:
+            ops.residual_add(self.x, self.pending2, 1.0)
+            self.pending2 = None
 
 
 class Block:
@@ -79,6 +89,7 @@ class PreNormBlock(Block):
 
     def forward(self, stream: ResidualStream, ctx, cache, owns_cache: bool) -> ResidualStream:
         rows, width = stream.x.shape
+        stream.flush_second()                      # (an arrangement that leaves two outputs may stand in front)
         few = rows <= ops.SKINNY_FAST_ROWS         # a step bound by the stream of weights: say early what comes next
         h = self.rt.buffer("normed", (rows, width))
         if few:
@@ -91,4 +102,32 @@ class PreNormBlock(Block):
         self.ffn_norm.forward(stream.x, h, delta=a, delta_scale=self.scale)
         f = self.ffn.forward(h, ctx)
         stream.pending, stream.pending_scale = f, self.scale
+        return stream
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    """parts: mixer_norm, mixer, and optionally ffn_norm + ffn; x <- x + (mixer(norm1(x)) + ffn(norm2(x))), both
+    norms of the same x. The two norms share their statistic (one mean of squares per row) and differ in their
+    weights only, so one kernel reads the row once, adds what the layer before left pending, and writes both
+    normalised rows (ops.rmsnorm_pair). Without a feed-forward the layer is x <- x + mixer(norm1(x))."""
+
+    def __init__(self, spec, store, runtime):
+        super().__init__(spec, store, runtime)
+        self.has_ffn = "ffn" in spec.parts
+        if self.has_ffn and float(spec.ffn_norm.eps) != float(spec.mixer_norm.eps):
+            from ..errors import Unsupported
+            raise Unsupported("parallel block: the two norms share one statistic and so one eps")
+
+    def forward(self, stream: ResidualStream, ctx, cache, owns_cache: bool) -> ResidualStream:
+        rows, width = stream.x.shape
+        if stream.pending is not None and stream.pending_scale != 1.0:
+            stream.flush()
+        h1 = self.rt.buffer("normed", (rows, width))
+        h2 = self.rt.buffer("normed_ffn", (rows, width)) if self.has_ffn else None
+        self.mixer_norm.forward_pair(stream.x, h1, self.ffn_norm if self.has_ffn else None, h2,
+                                     delta_a=stream.pending, delta_b=stream.pending2)
+        a = self.mixer.forward(h1, ctx, cache, owns_cache)
+        f = self.ffn.forward(h2, ctx) if self.has_ffn else None
+        stream.pending, stream.pending_scale, stream.pending2 = a, 1.0, f
         return stream

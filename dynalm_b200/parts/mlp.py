@@ -1,5 +1,6 @@
 """Gated feed-forward: down(act(gate x) * up x), the "gated_mlp" kind
-(dynalm/src/model/transformer.cpp:671-693). Gate and up run as one product against [Wg; Wu]."""
+(dynalm/src/model/transformer.cpp:671-693). Gate and up run as one product against [Wg; Wu].
+Ungated feed-forward: down(act(up x)), the "mlp" kind, act the squared ReLU."""
 
 from __future__ import annotations
 
@@ -9,7 +10,7 @@ import torch
 
 from ..errors import Unsupported
 from ..kernels import ops
-from ..kernels.gemm import linear_partial, linear_swiglu
+from ..kernels.gemm import linear, linear_partial, linear_swiglu
 from .base import TensorDecl, register_feed_forward
 
 
@@ -43,4 +44,37 @@ class GatedMLP:
         if x.shape[0] <= ops.SKINNY_FAST_ROWS:
             ops.stream_ahead(self.w_down)              # taken by the gate | up product, read by the product after it
         act = linear_swiglu(x, self.w_gate_up, rt, s.inner)
+        return linear_partial(act, self.w_down, rt, "ffn_out")
+
+
+@register_feed_forward("mlp")
+class DenseMLP:
+    """down(act(up x)) without a gate (parameters inner, activation: "relu2" = max(z, 0)^2)."""
+
+    replay_safe = True     # all device work goes through the recorded launches of kernels/ops.py (engine/launch_memo.py)
+    graph_safe = True      # launches depend on row counts only
+
+    @staticmethod
+    def declare(spec) -> Dict[str, TensorDecl]:
+        return {
+            "up": TensorDecl((spec.inner, spec.width)),
+            "down": TensorDecl((spec.width, spec.inner)),
+        }
+
+    def __init__(self, spec, tensors: Dict[str, torch.Tensor], runtime):
+        if spec.get("activation", "relu2") != "relu2":
+            raise Unsupported(f"mlp: activation '{spec.get('activation')}' has no kernel (relu2 does)")
+        self.spec = spec
+        self.rt = runtime
+        self.w_up = tensors["up"]
+        self.w_down = tensors["down"]
+
+    def first_weights(self) -> torch.Tensor:
+        return self.w_up
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        s, rt = self.spec, self.rt
+        act = rt.buffer("ffn_act", (x.shape[0], s.inner))
+        linear(x, self.w_up, act)
+        ops.relu2(act, act)
         return linear_partial(act, self.w_down, rt, "ffn_out")

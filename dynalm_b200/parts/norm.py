@@ -30,3 +30,12 @@ class RMSNorm:
         `rows` picks a subset. Everything is computed in float32; `out` has the compute dtype."""
         ops.rmsnorm(residual, self.weight, self.eps, out, delta=delta, delta_scale=delta_scale, rows=rows)
         return out
+
+    def forward_pair(self, residual: torch.Tensor, out: torch.Tensor, other: Optional["RMSNorm"],
+                     other_out: Optional[torch.Tensor], delta_a: Optional[torch.Tensor] = None,
+                     delta_b: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+        """This norm and `other` (same width and eps, its own weight; may be None) of the same row, in one kernel:
+        residual += delta_a + delta_b (written back unless `rows` selects), out = norm * weight, other_out = norm *
+        other's weight."""
+        ops.rmsnorm_pair(residual, self.weight, out, other.weight if other is not None else None, other_out, self.eps,
+                         delta_a=delta_a, delta_b=delta_b, rows=rows)

@@ -3,7 +3,7 @@
 The reference keeps a static array of adapters looked up by id
 (dynalm/src/model/architecture.cpp:112-125) and keys Hugging Face folders on `model_type`
 (dynalm/src/loader/hf/hf_model.cpp:160-171). Here the key is `architectures[0]` of
-config.json, with `model_type` as the fallback when that list is absent.
+config.json (or the string `architecture`), with `model_type` as the fallback when both are absent.
 """
 
 from __future__ import annotations
@@ -51,6 +51,13 @@ def find_architecture(config_obj: Mapping[str, Any]) -> Architecture:
         arch = _ARCHITECTURES.get(names[0])
         if arch is None:
             raise Unsupported(f"architecture '{names[0]}' is not supported; registered: "
+                              f"{', '.join(registered_architectures())}")
+        return arch
+    single = config_obj.get("architecture")          # some folders name their one architecture as a plain string
+    if isinstance(single, str):
+        arch = _ARCHITECTURES.get(single)
+        if arch is None:
+            raise Unsupported(f"architecture '{single}' is not supported; registered: "
                               f"{', '.join(registered_architectures())}")
         return arch
     model_type = config_obj.get("model_type")
