@@ -32,6 +32,11 @@ _SIGNATURES = {
     "qk_norm_cache": {
         "dl_qk_norm_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _L, _I, _I, _P, _P, _F, _F, _I, _I, _I, _I, _I, _I,
                                    _I, _I, _P]},
+    "attention_diff_flash": {
+        "dl_diff_attention_prefill": [_P, _I, _P, _L, _I, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _F, _F,
+                                      _P],
+        "dl_diff_attention_decode": [_P, _I, _P, _L, _I, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P,
+                                     _F, _F, _I, _P]},
     "attention_diff": {
         "dl_diff_attention": [_I, _P, _I, _P, _L, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P,
                               _F, _F, _P]},
@@ -543,6 +548,70 @@ def diff_attention(q: torch.Tensor, cache: torch.Tensor, k_off: int, v_off: int,
         dtype_code(q.dtype), _p(q), q.stride(0), _p(cache), cache.shape[2], k_off, v_off, _p(block_table),
         block_table.stride(0), _p(positions), _p(row_slot), _p(out), out.stride(0), q.shape[0], n_heads, n_kv_heads, dim,
         vdim, page_size, scale, softcap, _p(lam), out_scale, eps, _stream()), "diff_attention")
+
+
+def _diff_fast_checks(q, cache, out, block_table, lam, k_off, v_off, n_heads, n_kv_heads, dim, vdim, page_size, what):
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    if any(t.dtype != torch.bfloat16 for t in (q, cache, out)) or lam.dtype != torch.float32:
+        raise Unsupported(f"{what}: bfloat16 only (lambda float32)")
+    if dim % 16 or vdim % 16 or dim > 128 or vdim > 128 or n_heads % n_kv_heads or page_size & (page_size - 1):
+        raise Unsupported(f"{what}: dim {dim} and vdim {vdim} (multiples of 16 up to 128), heads {n_heads}:{n_kv_heads}, "
+                          f"page size {page_size} (a power of two)")
+    if cache.dim() != 3 or cache.shape[1] != page_size or not cache.is_contiguous() \
+            or k_off + n_kv_heads * 2 * dim > cache.shape[2] or v_off + n_kv_heads * vdim > cache.shape[2]:
+        raise InvalidArgument(f"{what}: the cache is not [pages, page_size, record] with room for keys and values")
+    if q.stride(0) % 8 or out.stride(0) % 2 or q.data_ptr() % 16 or out.data_ptr() % 4 or cache.data_ptr() % 16 \
+            or cache.shape[2] % 8 or k_off % 8 or v_off % 8:
+        raise Unsupported(f"{what}: q rows and records must be 16-byte aligned, out rows 4-byte aligned")
+    if block_table.dtype != torch.int32 or block_table.stride(-1) != 1:
+        raise InvalidArgument(f"{what}: block_table must be int32 rows")
+
+
+def diff_attention_prefill(q: torch.Tensor, cache: torch.Tensor, k_off: int, v_off: int, block_table: torch.Tensor,
+                           q_tiles: torch.Tensor, n_tiles: int, out: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int,
+                           vdim: int, page_size: int, scale: float, softcap: float, lam: torch.Tensor, out_scale: float,
+                           eps: float) -> None:
+    """Differential flash attention of query tiles over paged records, bfloat16; see csrc/attention_diff_flash.cu.
+    q_tiles: int32 [n_tiles, 4] = (request slot, first row, rows <= 128, first position)."""
+    _cuda(q, cache, block_table, q_tiles, out, lam)
+    _diff_fast_checks(q, cache, out, block_table, lam, k_off, v_off, n_heads, n_kv_heads, dim, vdim, page_size,
+                      "diff attention (prompt)")
+    if q_tiles.dtype != torch.int32 or q_tiles.numel() < 4 * n_tiles or q_tiles.data_ptr() % 16:
+        raise InvalidArgument("diff attention (prompt): q_tiles must be int32 [n_tiles, 4], 16-byte aligned")
+    check_limits("attention_diff_flash", pages=cache.shape[0], requests=block_table.shape[0], rows=q.shape[0])
+    _check(_fn("attention_diff_flash", "dl_diff_attention_prefill")(
+        _p(q), q.stride(0), _p(cache), cache.shape[2], k_off, v_off, _p(block_table), block_table.stride(0), _p(q_tiles),
+        n_tiles, _p(out), out.stride(0), n_heads, n_kv_heads, dim, vdim, page_size, scale, softcap, _p(lam), out_scale, eps,
+        _stream()), "diff_attention_prefill")
+
+
+def diff_decode_scratch_floats(rows: int, n_heads: int, vdim: int, n_split: int) -> int:
+    """Floats of scratch `diff_attention_decode` needs."""
+    return 0 if n_split <= 1 else rows * n_heads * n_split * 2 * (vdim + 2)
+
+
+def diff_attention_decode(q: torch.Tensor, cache: torch.Tensor, k_off: int, v_off: int, block_table: torch.Tensor,
+                          positions: torch.Tensor, row_slot: torch.Tensor, out: torch.Tensor, scratch: Optional[torch.Tensor],
+                          n_heads: int, n_kv_heads: int, dim: int, vdim: int, page_size: int, scale: float, softcap: float,
+                          lam: torch.Tensor, out_scale: float, eps: float, n_split: int) -> None:
+    """Differential split-KV attention for rows that bring one token each, bfloat16; see csrc/attention_diff_flash.cu.
+    `scratch`: float32 with at least diff_decode_scratch_floats(...) elements when n_split > 1."""
+    _cuda(q, cache, block_table, positions, row_slot, out, lam, scratch)
+    _diff_fast_checks(q, cache, out, block_table, lam, k_off, v_off, n_heads, n_kv_heads, dim, vdim, page_size,
+                      "diff attention (single tokens)")
+    rows = q.shape[0]
+    need = diff_decode_scratch_floats(rows, n_heads, vdim, n_split)
+    if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
+        raise InvalidArgument(f"diff attention (single tokens): scratch must be float32 with at least {need} elements")
+    check_limits("attention_diff_flash", pages=cache.shape[0], requests=block_table.shape[0], rows=rows)
+    _check(_fn("attention_diff_flash", "dl_diff_attention_decode")(
+        _p(q), q.stride(0), _p(cache), cache.shape[2], k_off, v_off, _p(block_table), block_table.stride(0), _p(positions),
+        _p(row_slot), _p(out), out.stride(0), _p(scratch), rows, n_heads, n_kv_heads, dim, vdim, page_size, scale, softcap,
+        _p(lam), out_scale, eps, int(n_split), _stream()), "diff_attention_decode")
+    if n_split > 1:
+        global LAUNCHES
+        LAUNCHES += 1          # the merge kernel
 
 
 def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, row_request: torch.Tensor,

@@ -90,6 +90,15 @@ class DiffAttention:
     def first_weights(self) -> torch.Tensor:
         return self.w_qkv
 
+    def step_plans(self) -> list:
+        """The query tiles of the step, for the prompt kernel (kernels/diff_attention.py)."""
+        from ..kernels import diff_attention as fast
+        return fast.step_plans()
+
+    def graph_key(self, ctx) -> tuple:
+        from ..kernels import diff_attention as fast
+        return (("diff_splits", fast.split_count(ctx.num_tokens, self.spec.num_heads, self.spec.num_kv_heads, ctx.max_kv_len)),)
+
     def cache_spec(self) -> Optional[CacheSpec]:
         """One record per token: the normalised keys of every KV head and map, then the values."""
         if not self.own_kv:
@@ -120,6 +129,9 @@ class DiffAttention:
     def attend(self, qkv: torch.Tensor, cache, ctx, out: torch.Tensor) -> None:
         s = self.spec
         (records,) = cache.arrays
+        from ..kernels import diff_attention as fast
+        if fast.attend(qkv, cache, ctx, out, s, self.lam, self.out_scale, self.eps, self.rt):
+            return
         ops.diff_attention(qkv, records, 0, self.k_width, cache.block_table, ctx.positions, ctx.row_slot, out,
                            s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, cache.page_size, float(s.scale),
                            float(s.get("softcap", 0.0)), self.lam, self.out_scale, self.eps)
