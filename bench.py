@@ -325,6 +325,123 @@ def long_prompt(tokens=32768, portion=512):
     return round(tokens / dt, 1), round(dt * 1e3, 1)
 
 
+# --workload todupel: the Todupel design beside the Llama shape of equal size. A pair shares width, layers, vocabulary,
+# query heads and KV heads; a Llama head is as wide as a Todupel head's two score maps together (head_dim = 2 * dim),
+# the value size equals it (vdim = 2 * dim), and the ungated feed-forward is 1.5 times as wide as the gated one, so
+# that every matrix product of a layer has the same number of weights on both sides.
+ARCH_SIZES = {
+    # name: (width, layers, heads, kv_heads, map size, llama intermediate size)
+    "w2048_d64": (2048, 4, 16, 4, 64, 8192),
+    "w4096_d64": (4096, 2, 32, 8, 64, 14336),
+    "w2048_d32": (2048, 4, 32, 8, 32, 8192),
+}
+ARCH_VOCAB = 32000
+
+
+def arch_pair(name):
+    width, layers, heads, kv, dim, inter = ARCH_SIZES[name]
+    mixer = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": 2 * dim, "scale": dim ** -0.5, "softcap": 50.0, "diff": 0.5,
+             "q_temp": {"coef": 0.3, "every": 128}}
+    todupel = {"architecture": "Todupel", "vocab": ARCH_VOCAB, "width": width, "norm": {"eps": 1e-5},
+               "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": {"kind": "dense", "ff": inter * 3 // 2}}
+                          for _ in range(layers)]}
+    llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": ARCH_VOCAB, "hidden_size": width,
+             "intermediate_size": inter, "num_hidden_layers": layers, "num_attention_heads": heads,
+             "num_key_value_heads": kv, "head_dim": 2 * dim, "max_position_embeddings": 8192, "rms_norm_eps": 1e-5,
+             "rope_theta": 500000.0, "tie_word_embeddings": False}
+    return todupel, llama
+
+
+def arch_compare(args, kernels: bool):
+    """Prefill (one prompt of 2,048 tokens) and decode (batches of 8 and 64 holding 2,048 tokens each) of the Todupel design
+    and of the Llama shape of equal size, timed with CUDA events; with `kernels`, instead, the device time of every kernel
+    of one prefill step and of decode steps at batch 8 that run launch by launch. Prints one JSON line."""
+    if kernels:
+        os.environ["DYNALM_PDL"] = "0"          # every kernel's time its own: none starts beside the one in front of it
+    import numpy as np
+    import torch
+    from dynalm_b200 import Engine, StepEntry
+    from dynalm_b200.engine.profile import kernel_times
+    from dynalm_b200.kernels import ops
+
+    peaks = load_peaks()
+    T, HELD_HERE, K = 2048, 2048, max(8, min(args.steps, 64))
+    out = {"metric": "Todupel beside the Llama shape of equal size: prefill and decode tokens/s", "unit": "tokens/s",
+           "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights, random token ids", "peaks": peaks,
+           "config": {"prefill_tokens": T, "decode_context": HELD_HERE, "decode_steps": K, "vocab": ARCH_VOCAB,
+                      "l2": "inputs larger than L2: the weights of a model exceed 126 MB"}, "sizes": {}}
+    rng = np.random.RandomState(0)
+    for size in ARCH_SIZES:
+        width, layers, heads, kv, dim, inter = ARCH_SIZES[size]
+        rec = {"shape": {"width": width, "layers": layers, "heads": heads, "kv_heads": kv, "map_size": dim,
+                         "value_size": 2 * dim, "llama_head_dim": 2 * dim, "llama_intermediate": inter,
+                         "todupel_ff": inter * 3 // 2}}
+        for which, cfg in zip(("todupel", "llama"), arch_pair(size)):
+            batches = (8,) if kernels else (8, 64)
+            span = 16 + 3 * K + 64
+            kv_tokens = max(batches) * (-(-(HELD_HERE + span) // 16) * 16) + 2 * T
+            eng = Engine(config=cfg, random_seed=1, dtype="bfloat16", ctx=kv_tokens, batch=T, max_running=max(batches))
+            step_fn = eng.step_fn
+            prompt = [int(t) for t in rng.randint(0, ARCH_VOCAB, T)]
+            ids_out = torch.zeros(max(batches), dtype=torch.int32, device="cuda:0")
+
+            def prefill_once():
+                step_fn.step([StepEntry("p", prompt, [T - 1])])
+                step_fn.end("p")
+
+            def fill(B):
+                for r in range(B):
+                    step_fn.step([StepEntry(("d", r), [int(t) for t in rng.randint(0, ARCH_VOCAB, HELD_HERE)], [])])
+
+            def decode_once(B):
+                logits = step_fn.step([StepEntry(("d", r), [7 + r], [0]) for r in range(B)], choose=(ids_out[:B], None))
+                if logits is not None:
+                    ops.argmax(logits, ids_out[:B])
+
+            def timed(fn, n):
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(n):
+                    fn()
+                b.record()
+                torch.cuda.synchronize()
+                return a.elapsed_time(b)
+
+            m = {}
+            for _ in range(3):
+                prefill_once()
+            if kernels:
+                with kernel_times(step_fn) as times:
+                    prefill_once()
+                m["prefill_kernels_ms"] = {k: [n, round(ms, 4)] for k, (n, ms) in times.totals().items()}
+                fill(8)
+                for _ in range(4):
+                    decode_once(8)
+                with kernel_times(step_fn) as times:
+                    for _ in range(4):
+                        decode_once(8)
+                m["decode_b8_kernels_ms_per_step"] = {k: [n // 4, round(ms / 4, 4)] for k, (n, ms) in times.totals().items()}
+            else:
+                ms = statistics.median(timed(prefill_once, 3) / 3 for _ in range(3))
+                m["prefill"] = {"tokens_per_s": round(T / ms * 1e3, 1), "ms": round(ms, 3)}
+                for B in batches:
+                    fill(B)
+                    for _ in range(16 + 3):
+                        decode_once(B)
+                    ms = statistics.median(timed(lambda: decode_once(B), K) / K for _ in range(3))
+                    m[f"decode_b{B}"] = {"tokens_per_s": round(B / ms * 1e3, 1), "ms_per_step": round(ms, 4)}
+                    for r in range(B):
+                        step_fn.end(("d", r))
+            rec[which] = m
+            del eng, step_fn
+            torch.cuda.empty_cache()
+        out["sizes"][size] = rec
+        print(f"[bench] {size} done", file=sys.stderr)
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -333,8 +450,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", choices=["decode"] + sorted(SERVING), default="decode",
-                    help="decode: the default benchmark; serve3b / serve8b: continuous batching of the 3B / 8B workloads")
+    ap.add_argument("--workload", choices=["decode", "todupel", "todupel-kernels"] + sorted(SERVING), default="decode",
+                    help="decode: the default benchmark; serve3b / serve8b: continuous batching of the 3B / 8B workloads; "
+                         "todupel: the Todupel design beside the Llama shape of equal size (todupel-kernels: per kernel)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-long", action="store_true", help="skip the points at 8,192 tokens (prefill and decode)")
     ap.add_argument("--no-serve", action="store_true", help="skip the points of the 3B and 8B serving workloads")
@@ -349,6 +467,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload in ("todupel", "todupel-kernels"):
+        return arch_compare(args, kernels=args.workload == "todupel-kernels")
     if args.workload != "decode":
         return serving(args.workload, args.layers if args.layers != FULL_LAYERS else None)
     W = max(3, args.warmup)

@@ -191,19 +191,21 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
   const int CHV = vd / 8;
   const size_t k_at = static_cast<size_t>(a.k_off) + static_cast<size_t>(kvh) * 2 * dim;
   const size_t v_at = static_cast<size_t>(a.v_off) + static_cast<size_t>(kvh) * vd;
+  // Two threads copy one key's record: its page is looked up once per tile and thread, and the 16-byte pieces of the
+  // key's two maps and of its values go out without another dependent load in between.
+  const int kv_r = tid >> 1, kv_half = tid & 1;
+  const uint32_t k_row = static_cast<uint32_t>(kv_r * LDQ * sizeof(bf16)), v_row = static_cast<uint32_t>(kv_r * LDV * sizeof(bf16));
   auto load_kv = [&](int j, int stage) {
-    const uint32_t k_stage = ks_base + static_cast<uint32_t>(stage * DF_BN * LDQ * sizeof(bf16));
-    const uint32_t v_stage = vs_base + static_cast<uint32_t>(stage * DF_BN * LDV * sizeof(bf16));
-    const int per_key = CHQ + CHV;
-    for (int c = tid; c < DF_BN * per_key; c += DF_THREADS) {
-      const int r = c / per_key, ch = c % per_key;
-      const int key = j * DF_BN + r;
-      const bool ok = key <= pos_last;
-      size_t rec = 0;
-      if (ok) rec = ((static_cast<size_t>(ck_page(table, key >> a.page_shift, a.max_blocks)) << a.page_shift) + (key & page_mask)) * a.record;
-      if (ch < CHQ) df_cp16(k_stage + static_cast<uint32_t>((r * LDQ + ch * 8) * sizeof(bf16)), a.cache + rec + k_at + ch * 8, ok);
-      else df_cp16(v_stage + static_cast<uint32_t>((r * LDV + (ch - CHQ) * 8) * sizeof(bf16)), a.cache + rec + v_at + (ch - CHQ) * 8, ok);
-    }
+    const uint32_t k_stage = ks_base + static_cast<uint32_t>(stage * DF_BN * LDQ * sizeof(bf16)) + k_row;
+    const uint32_t v_stage = vs_base + static_cast<uint32_t>(stage * DF_BN * LDV * sizeof(bf16)) + v_row;
+    const int key = j * DF_BN + kv_r;
+    const bool ok = key <= pos_last;
+    size_t rec = 0;
+    if (ok) rec = ((static_cast<size_t>(ck_page(table, key >> a.page_shift, a.max_blocks)) << a.page_shift) + (key & page_mask)) * a.record;
+    const bf16* ksrc = a.cache + rec + k_at;
+    const bf16* vsrc = a.cache + rec + v_at;
+    for (int ch = kv_half; ch < CHQ; ch += 2) df_cp16(k_stage + ch * 16, ksrc + ch * 8, ok);
+    for (int ch = kv_half; ch < CHV; ch += 2) df_cp16(v_stage + ch * 16, vsrc + ch * 8, ok);
   };
   if (j_begin <= j_end) load_kv(j_begin, 0);
   df_commit();

@@ -38,7 +38,7 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-enum { SK_OUT_BF16 = 0, SK_OUT_F32 = 1, SK_OUT_SWIGLU = 2, SK_OUT_ARGMAX = 3 };
+enum { SK_OUT_BF16 = 0, SK_OUT_F32 = 1, SK_OUT_SWIGLU = 2, SK_OUT_ARGMAX = 3, SK_OUT_RELU2 = 4 };
 
 // The weight stream of one block: y^T tile = W rows (wrow, 16 * MT of them in MMA row order) times x^T, k-blocks
 // [blk_begin, blk_end) dealt to the warps round-robin. Leaves every warp's partial tile in `red`
@@ -233,8 +233,13 @@ gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
     v *= out_scale;
     if (mode == SK_OUT_F32)
       static_cast<float*>(y)[static_cast<size_t>(split) * split_stride + static_cast<size_t>(b) * ldy + f] = v;
-    else
+    else {
+      if (mode == SK_OUT_RELU2) {        // the squared ReLU of an ungated feed-forward
+        v = fmaxf(v, 0.0f);
+        v *= v;
+      }
       static_cast<bf16*>(y)[static_cast<size_t>(b) * ldy + f] = __float2bfloat16_rn(v);
+    }
   }
 }
 
@@ -331,7 +336,7 @@ int launch_skinny(const void* x, int ldx, const void* w, void* y, int ldy, int M
 // x: bf16 [M, K] rows of ldx elements (16-byte aligned rows), w: bf16 [N, K] contiguous, K a multiple of 8,
 // M <= 64. mode 0: y bf16 [M, N]; mode 1: y fp32, n_split partial results of [M, ldy] floats each,
 // split_stride floats apart; mode 2: w = [gate; up] (N even), y bf16 [M, N / 2] = silu(x Wg^T) * (x Wu^T).
-// mode 3: nothing but the place of each row's largest output leaves the kernel: y = float [M][blocks] then
+// mode 4: y bf16 [M, N] = max(x W^T, 0)^2. mode 3: nothing but the place of each row's largest output leaves the kernel: y = float [M][blocks] then
 // int [M][blocks] (blocks = ceil(N / features per block), see dl_gemm_skinny_argmax_blocks), the largest value of every
 // block's features and its feature index (the lowest among equals); out_scale must be positive.
 // n_split > 1 needs mode 1. ahead, ahead_bytes: memory that the kernel after this one will stream (weights),
@@ -341,7 +346,7 @@ DL_EXPORT int dl_gemm_skinny(const void* x, int ldx, const void* w, void* y, int
                              long long ahead_bytes, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64 || K <= 0 || (K & 7) || (ldx & 7) || n_split < 1 || n_split > 64 || (n_split > 1 && mode != dl::SK_OUT_F32) ||
-      (mode == dl::SK_OUT_SWIGLU && (N & 1)) || mode < 0 || mode > 3 || (mode == dl::SK_OUT_ARGMAX && !(out_scale > 0.0f)))
+      (mode == dl::SK_OUT_SWIGLU && (N & 1)) || mode < 0 || mode > 4 || (mode == dl::SK_OUT_ARGMAX && !(out_scale > 0.0f)))
     return DL_ERR_UNSUPPORTED;
   if (M <= 8) return dl::launch_skinny<1, 1>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, ahead, ahead_bytes, stream);
   if (M <= 16) return dl::launch_skinny<1, 2>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, ahead, ahead_bytes, stream);

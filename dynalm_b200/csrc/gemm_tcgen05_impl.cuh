@@ -23,7 +23,7 @@ template <int BN> struct T5 {
   static constexpr size_t SMEM = static_cast<size_t>(STAGES) * STAGE_BYTES + T5_STORE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
 
-enum { T5_OUT_BF16 = 0, T5_OUT_F32 = 1, T5_OUT_SWIGLU = 2, T5_OUT_QKV_ROPE = 3 };
+enum { T5_OUT_BF16 = 0, T5_OUT_F32 = 1, T5_OUT_SWIGLU = 2, T5_OUT_QKV_ROPE = 3, T5_OUT_RELU2 = 4 };
 enum { T5_ERR_PRODUCER = 1, T5_ERR_MMA = 2, T5_ERR_EPILOGUE = 3 };
 
 // Which output tile a tile number stands for. Tiles are numbered in groups of `group_m` row blocks: inside a
@@ -336,17 +336,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
               }
             }
           } else {
+            // bf16 out; with T5_OUT_RELU2 the squared ReLU of an ungated feed-forward on the way
+            const bool relu2 = mode == T5_OUT_RELU2;
+            auto fin = [&](uint32_t u) {
+              float x = __uint_as_float(u) * out_scale;
+              if (relu2) {
+                x = fmaxf(x, 0.0f);
+                x *= x;
+              }
+              return x;
+            };
             uint4 w[8];
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
               const uint32_t* v = hh == 0 ? va : vb;
 #pragma unroll
               for (int j = 0; j < 32; j += 8)
-                w[hh * 4 + j / 8] = make_uint4(
-                    pack2_bf16(__uint_as_float(v[j]) * out_scale, __uint_as_float(v[j + 1]) * out_scale),
-                    pack2_bf16(__uint_as_float(v[j + 2]) * out_scale, __uint_as_float(v[j + 3]) * out_scale),
-                    pack2_bf16(__uint_as_float(v[j + 4]) * out_scale, __uint_as_float(v[j + 5]) * out_scale),
-                    pack2_bf16(__uint_as_float(v[j + 6]) * out_scale, __uint_as_float(v[j + 7]) * out_scale));
+                w[hh * 4 + j / 8] = make_uint4(pack2_bf16(fin(v[j]), fin(v[j + 1])), pack2_bf16(fin(v[j + 2]), fin(v[j + 3])),
+                                               pack2_bf16(fin(v[j + 4]), fin(v[j + 5])), pack2_bf16(fin(v[j + 6]), fin(v[j + 7])));
             }
             store_rows_bf16(w, my_stage, lane, static_cast<bf16*>(y), ldy, row0, M, n0 + c0, N);   // N is a multiple of 8
           }
@@ -388,14 +395,14 @@ static inline int make_map(CUtensorMap* map, const void* base, int rows, int col
 
 // x: bf16 [M, K] rows of ldx elements; w: bf16 [N, K] contiguous; both 16-byte aligned with K and ldx multiples of 8.
 // mode 0: y bf16 [M, N] (N % 8 == 0); mode 1: y fp32 [M, N] (N % 4 == 0); mode 2: w = [gate; up] with N = 2F rows,
-// y bf16 [M, F] = silu(x Wg^T) * (x Wu^T) (F % 8 == 0). status: one device int, set to a nonzero code if a wait
+// y bf16 [M, F] = silu(x Wg^T) * (x Wu^T) (F % 8 == 0); mode 4: y bf16 [M, N] = max(x W^T, 0)^2. status: one device int, set to a nonzero code if a wait
 // inside the kernel timed out (left untouched otherwise).
 template <class P>
 static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode, float out_scale,
                      int* status, const dl::QkvRope& rope, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
-      status == nullptr || mode < 0 || mode > 3)
+      status == nullptr || mode < 0 || mode > 4)
     return DL_ERR_UNSUPPORTED;
   const int feats = mode == dl::T5_OUT_SWIGLU ? N / 2 : N;
   if ((mode == dl::T5_OUT_SWIGLU && (N & 1)) || (mode == dl::T5_OUT_F32 ? (feats & 3) || (ldy & 3) : (feats & 7) || (ldy & 7)) ||

@@ -203,6 +203,65 @@ __global__ void rmsnorm_pair_kernel(float* __restrict__ x, const void* __restric
   }
 }
 
+// The pair norm with the row held in registers: 16-byte accesses, one pass over global memory. Widths that are a
+// multiple of 4 up to NV * 1024, part strides that are multiples of 4.
+__device__ __forceinline__ float4 delta4_any(const void* p, int dtype, size_t i, int parts, size_t part_stride) {
+  float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (p == nullptr) return d;
+  for (int q = 0; q < parts; ++q) {
+    const float4 e = dtype == 0 ? load4<float>(static_cast<const float*>(p) + q * part_stride + i)
+                                : load4<bf16>(static_cast<const bf16*>(p) + q * part_stride + i);
+    d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+  }
+  return d;
+}
+
+template <typename TO, int NV>
+__global__ void __launch_bounds__(NORM_VEC_THREADS)
+rmsnorm_pair_vec_kernel(float* __restrict__ x, const void* __restrict__ delta_a, int dtype_a, int parts_a, size_t stride_a,
+                        const void* __restrict__ delta_b, int dtype_b, int parts_b, size_t stride_b,
+                        const float* __restrict__ w_a, const float* __restrict__ w_b, float eps, TO* __restrict__ out_a,
+                        TO* __restrict__ out_b, const int* __restrict__ rows, int width, int write_residual) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const size_t src = rows ? static_cast<size_t>(ck_row(rows[r])) : static_cast<size_t>(r);
+  float* xr = x + src * width;
+  const bool any = delta_a != nullptr || delta_b != nullptr;
+  float4 v[NV];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * NORM_VEC_THREADS + threadIdx.x) * 4;
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < width) {
+      v[i] = load4<float>(xr + c);
+      if (any) {
+        const float4 da = delta4_any(delta_a, dtype_a, src * width + c, parts_a, stride_a);
+        const float4 db = delta4_any(delta_b, dtype_b, src * width + c, parts_b, stride_b);
+        v[i].x += da.x + db.x; v[i].y += da.y + db.y; v[i].z += da.z + db.z; v[i].w += da.w + db.w;
+        if (write_residual) store4<float>(xr + c, v[i]);
+      }
+    }
+    ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+    ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * NORM_VEC_THREADS + threadIdx.x) * 4;
+    if (c < width) {
+      const float4 n = make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv);
+      const float4 ga = load4<float>(w_a + c);
+      store4<TO>(out_a + static_cast<size_t>(r) * width + c, make_float4(n.x * ga.x, n.y * ga.y, n.z * ga.z, n.w * ga.w));
+      if (out_b != nullptr) {
+        const float4 gb = load4<float>(w_b + c);
+        store4<TO>(out_b + static_cast<size_t>(r) * width + c, make_float4(n.x * gb.x, n.y * gb.y, n.z * gb.z, n.w * gb.w));
+      }
+    }
+  }
+}
+
 // x += scale * delta, for a pending residual that no norm follows.
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, float scale, size_t n,
@@ -278,6 +337,28 @@ DL_EXPORT int dl_rmsnorm_pair(int out_dtype, float* x, const void* delta_a, int 
   if (n_rows <= 0) return 0;
   if ((dtype_a != 0 && dtype_a != 1) || (dtype_b != 0 && dtype_b != 1) || (out_b != nullptr && w_b == nullptr))
     return DL_ERR_UNSUPPORTED;
+  if (width % 4 == 0 && width <= 8 * 4 * dl::NORM_VEC_THREADS && stride_a % 4 == 0 && stride_b % 4 == 0 &&
+      (reinterpret_cast<uintptr_t>(delta_a) & 15) == 0 && (reinterpret_cast<uintptr_t>(delta_b) & 15) == 0 &&
+      (out_dtype == 0 || out_dtype == 1)) {
+    const int nv = (width + 4 * dl::NORM_VEC_THREADS - 1) / (4 * dl::NORM_VEC_THREADS);
+#define DL_PAIR(TO, NV)                                                                                                \
+  dl::rmsnorm_pair_vec_kernel<TO, NV><<<n_rows, dl::NORM_VEC_THREADS, 0, stream>>>(                                    \
+      x, delta_a, dtype_a, parts_a, static_cast<size_t>(stride_a), delta_b, dtype_b, parts_b,                          \
+      static_cast<size_t>(stride_b), w_a, w_b, eps, static_cast<TO*>(out_a), static_cast<TO*>(out_b), rows, width,     \
+      write_residual)
+#define DL_PAIR_NV(TO)                    \
+  do {                                    \
+    if (nv <= 1) DL_PAIR(TO, 1);          \
+    else if (nv <= 2) DL_PAIR(TO, 2);     \
+    else if (nv <= 4) DL_PAIR(TO, 4);     \
+    else DL_PAIR(TO, 8);                  \
+  } while (0)
+    if (out_dtype == 0) DL_PAIR_NV(float);
+    else DL_PAIR_NV(dl::bf16);
+#undef DL_PAIR_NV
+#undef DL_PAIR
+    return dl::launch_status();
+  }
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
 #define DL_LAUNCH(TO)                                                                                               \
   dl::rmsnorm_pair_kernel<TO><<<n_rows, threads, 0, stream>>>(                                                      \

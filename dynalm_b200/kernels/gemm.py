@@ -172,3 +172,23 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, runtime, inner: int)
     linear(x, w_gate_up, gate_up)
     ops.silu_mul(gate_up, act)
     return act
+
+
+def linear_relu2(x: torch.Tensor, w_up: torch.Tensor, runtime, inner: int) -> torch.Tensor:
+    """max(x W^T, 0)^2, the first half of an ungated feed-forward: the activation sits in the product's epilogue
+    wherever one of this package's bfloat16 kernels runs the product, else the product is followed by the
+    activation kernel (float32, and the few shapes that go to the library)."""
+    rows = x.shape[0]
+    act = runtime.buffer("ffn_act", (rows, inner))
+    if x.dtype == torch.bfloat16 and use_stream(x, w_up):
+        ops.gemm_stream(x, w_up, act, "relu2")
+        return act
+    if x.dtype == torch.bfloat16 and skinny_ok(x, w_up):
+        ops.gemm_skinny(x, w_up, act, "relu2")
+        return act
+    if x.dtype == torch.bfloat16 and tcgen05_ok(x, w_up, act, inner):
+        ops.gemm_tcgen05(x, w_up, act, "relu2")
+        return act
+    linear(x, w_up, act)
+    ops.relu2(act, act)
+    return act

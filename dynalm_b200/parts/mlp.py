@@ -10,7 +10,7 @@ import torch
 
 from ..errors import Unsupported
 from ..kernels import ops
-from ..kernels.gemm import linear, linear_partial, linear_swiglu
+from ..kernels.gemm import linear_partial, linear_relu2, linear_swiglu
 from .base import TensorDecl, register_feed_forward
 
 
@@ -74,7 +74,7 @@ class DenseMLP:
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         s, rt = self.spec, self.rt
-        act = rt.buffer("ffn_act", (x.shape[0], s.inner))
-        linear(x, self.w_up, act)
-        ops.relu2(act, act)
+        if x.shape[0] <= ops.SKINNY_FAST_ROWS:
+            ops.stream_ahead(self.w_down)              # taken by the up product, read by the product after it
+        act = linear_relu2(x, self.w_up, rt, s.inner)
         return linear_partial(act, self.w_down, rt, "ffn_out")

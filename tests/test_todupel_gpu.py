@@ -203,7 +203,7 @@ def test_differential_attention_where_one_key_carries_the_score(dtype, heads, gr
 def test_pair_norm_adds_both_pending_outputs_and_shares_one_statistic(dtype):
     from dynalm_b200.kernels import ops
     rng = np.random.RandomState(5)
-    for width, rows in ((96, 5), (100, 3), (2048, 2)):
+    for width, rows in ((96, 5), (100, 3), (90, 4), (2048, 2), (5000, 2)):
         x = torch.from_numpy(rng.randn(rows, width)).to(DEV, torch.float32)
         da = torch.from_numpy(rng.randn(rows, width)).to(DEV, dtype)
         db = torch.from_numpy(rng.randn(3, rows, width)).to(DEV, torch.float32)       # partial sums of a split product
@@ -246,6 +246,23 @@ def test_squared_relu_feed_forward(dtype, rows):
         want = plain.relu2_mlp(x.double().cpu().numpy(), up.double().cpu().numpy(), down.double().cpu().numpy())
         tol = 1e-4 if dtype == torch.float32 else 6e-2
         assert np.abs(got.cpu().numpy() - want).max() <= tol * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("rows,inner,width", [(4, 272, 256), (12, 272, 256), (40, 272, 256), (1024, 2048, 256), (300, 4096, 512)])
+def test_squared_relu_in_the_epilogue_of_every_product_kernel(rows, inner, width):
+    """max(x W^T, 0)^2 by whichever kernel the dispatcher picks for the shape (few rows: the weight-streaming ones; many
+    tiles: the tcgen05 one; in between the library followed by the activation kernel) against the plain product."""
+    from dynalm_b200.engine.runtime import Runtime
+    from dynalm_b200.kernels.gemm import linear_relu2
+    rng = np.random.RandomState(rows)
+    rt = Runtime(DEV, torch.bfloat16, max_tokens=1024)
+    x = torch.from_numpy(rng.randn(rows, width)).to(DEV, torch.bfloat16)
+    w = torch.from_numpy(rng.randn(inner, width) * 0.1).to(DEV, torch.bfloat16)
+    got = linear_relu2(x, w, rt, inner).double().cpu().numpy()
+    z = np.maximum(x.double().cpu().numpy() @ w.double().cpu().numpy().T, 0.0)
+    want = z * z
+    assert np.abs(got - want).max() <= 1e-2 * max(1.0, np.abs(want).max())
+    assert (got >= 0).all() and (got[want == 0] == 0).all()
 
 
 # ---------------------------------------------------------------------------------------------
@@ -334,12 +351,26 @@ def test_greedy_generation_through_the_engine(name, folders):
             assert row[tok] >= row.max() - 2e-5, f"token {i}: chose {tok} at {row[tok]:.6f}, best {row.max():.6f}"
     alone = [eng.generate(p, max_tokens=12).tokens for p in reqs.values()]
     assert alone == [g.tokens for g in outs]
-    # so few pages that requests are preempted and recomputed: the same tokens
-    longer = [g.tokens for g in eng.generate(list(reqs.values()), max_tokens=40)]
-    tight = Engine(folder, dtype="float32", ctx=160, batch=64, max_running=4)
-    again = tight.generate(list(reqs.values()), max_tokens=40)
-    assert [g.tokens for g in again] == longer and [t[:12] for t in longer] == [g.tokens for g in outs]
-    assert tight.scheduler.stats.preemptions > 0
+
+
+def test_few_pages_give_the_same_tokens(folders):
+    """An engine whose pool is too small for its requests preempts and recomputes, and gives the tokens of a roomy one."""
+    from dynalm_b200 import Engine, SchedulerConfig
+    name = "ta"
+    reqs = list(random_requests(TODUPEL[name][0]["vocab"], [40, 90, 17, 100, 64, 33], seed=15).values())
+
+    def run(ctx):
+        eng = Engine(folders["float32"][name], dtype="float32", ctx=ctx, batch=128, max_running=8,
+                     scheduler=SchedulerConfig(max_running=6, decode_token_budget=8, prefill_token_budget=64,
+                                               max_prefill_chunk=32, max_batch_tokens=128))
+        out = eng.generate(reqs, max_tokens=40)
+        assert eng.built.cache.free_pages == eng.built.cache.num_pages
+        return [g.tokens for g in out], eng.scheduler.stats.preemptions
+
+    roomy, p0 = run(4096)
+    tight, p1 = run(320)
+    assert p0 == 0 and p1 > 0
+    assert tight == roomy
 
 
 def test_command_line_generates(folders):
