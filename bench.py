@@ -14,7 +14,8 @@ leaves room for while the measurement grows them), and a prefill of 8,192 tokens
 of the roofline; last, the continuous-batching workloads of the 3B and 8B shapes (tokens/s over the whole run,
 median time to the first token, decode-only step), a 32,768-token prompt brought in portions of 512, and the
 end-to-end decode again with requests that draw their tokens (temperature, top-k, top-p, a penalty). `--workload serve3b | serve8b` runs one of those alone and
-prints its full record. Prints one JSON line.
+prints its full record; `--workload todupel` measures the Todupel design beside the Llama shape of equal size at three
+sizes (`todupel-kernels`: the device time of every kernel of both). Prints one JSON line.
 """
 
 import argparse

@@ -46,9 +46,16 @@ __device__ __forceinline__ float df_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// tanh(x) = 1 - 2 / (1 + e^(2x)): absolute error of a few 1e-7 over the whole range, exact limits at both ends.
-__device__ __forceinline__ float df_tanh(float x) {
-  return 1.0f - __fdividef(2.0f, 1.0f + df_exp2(x * (2.0f * DF_LOG2E)));
+__device__ __forceinline__ float df_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// c * tanh(x) = c - 2c / (1 + e^(2x)), with x2 = 2 x log2(e) and c2 = -2c given: absolute error of a few 1e-7 of c
+// over the whole range, exact limits at both ends (e^(2x) = inf gives c, 0 gives -c). Four instructions, two of them on
+// the special-function unit.
+__device__ __forceinline__ float df_scaled_tanh(float x2, float c, float c2) {
+  return fmaf(df_rcp(1.0f + df_exp2(x2)), c2, c);
 }
 __device__ __forceinline__ uint32_t df_pack(float lo, float hi) {
   __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
@@ -78,27 +85,34 @@ struct DiffParams {
 };
 
 // A part of a (row, head): per map (max in log2 units, sum, acc[vd]), 2 * (vd + 2) floats. Merges `n` parts that lie
-// `stride` floats apart into lane-held values: every lane ends with the merged (max, sum) of both maps and the
+// `stride` floats apart (n at most 32) into lane-held values: every lane ends with the merged (max, sum) of both maps and the
 // acc of its own value columns d = lane, lane + 32, ...
 template <int VDMAX>
 __device__ __forceinline__ void df_merge_parts(const float* parts, int n, size_t stride, int vd, int lane, float (&mx)[2],
                                                float (&sum)[2], float (&acc)[2][VDMAX / 32 > 0 ? VDMAX / 32 : 1]) {
   constexpr int PL = VDMAX / 32 > 0 ? VDMAX / 32 : 1;
+  // lane p holds part p's (max, sum) of both maps (n <= 32): the merged max and sum are two butterflies, and the
+  // loads of the accumulators below depend on nothing but their addresses
+  float w[2];
 #pragma unroll
   for (int m = 0; m < 2; ++m) {
-    mx[m] = -INFINITY;
-    for (int p = 0; p < n; ++p) mx[m] = fmaxf(mx[m], parts[p * stride + m * (vd + 2)]);
-    sum[m] = 0.0f;
+    const float pm = lane < n ? parts[lane * stride + m * (vd + 2)] : -INFINITY;
+    const float pl = lane < n ? parts[lane * stride + m * (vd + 2) + 1] : 0.0f;
+    mx[m] = warp_max(pm);
+    w[m] = pm == -INFINITY ? 0.0f : df_exp2(pm - mx[m]);
+    sum[m] = warp_sum(pl * w[m]);
 #pragma unroll
     for (int i = 0; i < PL; ++i) acc[m][i] = 0.0f;
-    for (int p = 0; p < n; ++p) {
-      const float* part = parts + p * stride + m * (vd + 2);
-      const float w = part[0] == -INFINITY ? 0.0f : df_exp2(part[0] - mx[m]);
-      sum[m] = fmaf(part[1], w, sum[m]);
+  }
+  for (int p = 0; p < n; ++p) {
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+      const float wp = __shfl_sync(0xffffffffu, w[m], p);
+      const float* part = parts + p * stride + m * (vd + 2) + 2;
 #pragma unroll
       for (int i = 0; i < PL; ++i) {
         const int d = lane + 32 * i;
-        if (d < vd) acc[m][i] = fmaf(part[2 + d], w, acc[m][i]);
+        if (d < vd) acc[m][i] = fmaf(part[d], wp, acc[m][i]);
       }
     }
   }
@@ -153,15 +167,17 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
     pos0 = positions[row0];
     nrows = 1;
   } else {
+    // heads are the fast index of the grid: the host lists the tiles that read the most keys first, so the longest
+    // blocks of all heads start first and the grid ends evenly
     constexpr int SUB = DF_TILE / DF_BM;
-    const int4 tile = ck_tile(tiles[blockIdx.x / SUB]);
-    const int sub = blockIdx.x % SUB;
+    const int4 tile = ck_tile(tiles[blockIdx.y / SUB]);
+    const int sub = blockIdx.y % SUB;
     req = tile.x;
     row0 = tile.y + sub * DF_BM;
     nrows = min(DF_BM, tile.z - sub * DF_BM);
     pos0 = tile.w + sub * DF_BM;
     if (nrows <= 0) return;
-    head0 = blockIdx.y;
+    head0 = blockIdx.x;
     kvh = head0 / group;
     nheads_here = 1;
   }
@@ -195,20 +211,26 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
   // key's two maps and of its values go out without another dependent load in between.
   const int kv_r = tid >> 1, kv_half = tid & 1;
   const uint32_t k_row = static_cast<uint32_t>(kv_r * LDQ * sizeof(bf16)), v_row = static_cast<uint32_t>(kv_r * LDV * sizeof(bf16));
-  auto load_kv = [&](int j, int stage) {
+  // the record of this thread's key of tile j (its number in the cache), -1 past the last key: looked up one
+  // tile before its copies are issued, so that no copy waits for its page id
+  auto find_record = [&](int j) -> int {
+    const int key = j * DF_BN + kv_r;
+    if (j > j_end || key > pos_last) return -1;
+    return (ck_page(table, key >> a.page_shift, a.max_blocks) << a.page_shift) + (key & page_mask);
+  };
+  auto load_kv = [&](int slot, int stage) {
+    const long long rec = static_cast<long long>(slot) * a.record;
     const uint32_t k_stage = ks_base + static_cast<uint32_t>(stage * DF_BN * LDQ * sizeof(bf16)) + k_row;
     const uint32_t v_stage = vs_base + static_cast<uint32_t>(stage * DF_BN * LDV * sizeof(bf16)) + v_row;
-    const int key = j * DF_BN + kv_r;
-    const bool ok = key <= pos_last;
-    size_t rec = 0;
-    if (ok) rec = ((static_cast<size_t>(ck_page(table, key >> a.page_shift, a.max_blocks)) << a.page_shift) + (key & page_mask)) * a.record;
-    const bf16* ksrc = a.cache + rec + k_at;
-    const bf16* vsrc = a.cache + rec + v_at;
+    const bool ok = slot >= 0;
+    const bf16* ksrc = a.cache + (ok ? rec : 0) + k_at;
+    const bf16* vsrc = a.cache + (ok ? rec : 0) + v_at;
     for (int ch = kv_half; ch < CHQ; ch += 2) df_cp16(k_stage + ch * 16, ksrc + ch * 8, ok);
     for (int ch = kv_half; ch < CHV; ch += 2) df_cp16(v_stage + ch * 16, vsrc + ch * 8, ok);
   };
-  if (j_begin <= j_end) load_kv(j_begin, 0);
+  if (j_begin <= j_end) load_kv(find_record(j_begin), 0);
   df_commit();
+  int rec_next = find_record(j_begin + 1);
 
   float o[2][VDMAX / 8][4];
 #pragma unroll
@@ -223,13 +245,18 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
   const int q_row = (SINGLE ? 0 : warp * 16) + (lane & 7) + ((lane >> 3) & 1) * 8;
   const int kg0 = SINGLE ? warp : 0;               // first 16-key group of a tile that this warp takes
   const float cap = a.softcap;
-  const float pre = cap > 0.0f ? a.scale / cap : a.scale * DF_LOG2E;   // raw score -> tanh argument, or -> log2 units
-  const float post = cap * DF_LOG2E;
+  // raw score -> 2 log2(e) times the tanh argument (capped), or -> log2 units (not capped); the capped score in log2 units
+  // is post * tanh
+  const float pre = cap > 0.0f ? a.scale / cap * (2.0f * DF_LOG2E) : a.scale * DF_LOG2E;
+  const float post = cap * DF_LOG2E, post2 = -2.0f * post;
   const int KS = dim / 16;
 
   for (int j = j_begin; j <= j_end; ++j) {
     const int stage = (j - j_begin) & 1;
-    if (j < j_end) load_kv(j + 1, stage ^ 1);
+    if (j < j_end) {
+      load_kv(rec_next, stage ^ 1);
+      rec_next = find_record(j + 2);
+    }
     df_commit();
     df_wait<1>();
     __syncthreads();
@@ -237,6 +264,7 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
     const bf16* vt = Vs + stage * DF_BN * LDV;
     const int key0 = j * DF_BN + kg0 * 16;
     const bool edge = key0 + NKG * 16 - 1 > (SINGLE ? pos0 : pos0 + warp * 16);
+    uint32_t pf[2][NKG][4];          // both maps' weights as bf16 A fragments
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
       float s[NKG * 2][4];
@@ -261,7 +289,7 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float v = s[i][e] * pre;
-          if (cap > 0.0f) v = df_tanh(v) * post;
+          if (cap > 0.0f) v = df_scaled_tanh(v, post, post2);
           if (edge) {
             const int key = key0 + i * 8 + 2 * t + (e & 1);
             if (key > ((e >> 1) ? pos_b : pos_a)) v = -INFINITY;
@@ -282,15 +310,14 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
         neg_m[h] = m_new == -INFINITY ? 0.0f : -m_new;
       }
       float ls[2] = {0.0f, 0.0f};
-      uint32_t pf[NKG][4];
 #pragma unroll
       for (int i = 0; i < NKG * 2; ++i) {
         const float p0 = df_exp2(s[i][0] + neg_m[0]), p1 = df_exp2(s[i][1] + neg_m[0]);
         const float p2 = df_exp2(s[i][2] + neg_m[1]), p3 = df_exp2(s[i][3] + neg_m[1]);
         ls[0] += p0 + p1;
         ls[1] += p2 + p3;
-        pf[i >> 1][(i & 1) * 2] = df_pack(p0, p1);
-        pf[i >> 1][(i & 1) * 2 + 1] = df_pack(p2, p3);
+        pf[m][i >> 1][(i & 1) * 2] = df_pack(p0, p1);
+        pf[m][i >> 1][(i & 1) * 2 + 1] = df_pack(p2, p3);
       }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -305,18 +332,20 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
           o[m][i][2] *= corr[1]; o[m][i][3] *= corr[1];
         }
       }
-      // O_m += P V
+    }
+    // O_m += P_m V for both maps: a value fragment is loaded once and serves both
 #pragma unroll
-      for (int kk = 0; kk < NKG; ++kk) {
+    for (int kk = 0; kk < NKG; ++kk) {
 #pragma unroll
-        for (int dp = 0; dp < VDMAX / 16; ++dp) {
-          if (dp * 16 < vd) {
-            uint32_t vb[4];
-            const int key = (kg0 + kk) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-            df_ldmatrix_x4_trans(vb, vt + key * LDV + dp * 16 + (lane >> 4) * 8);
-            df_mma(o[m][2 * dp], pf[kk], vb[0], vb[1]);
-            df_mma(o[m][2 * dp + 1], pf[kk], vb[2], vb[3]);
-          }
+      for (int dp = 0; dp < VDMAX / 16; ++dp) {
+        if (dp * 16 < vd) {
+          uint32_t vb[4];
+          const int key = (kg0 + kk) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          df_ldmatrix_x4_trans(vb, vt + key * LDV + dp * 16 + (lane >> 4) * 8);
+          df_mma(o[0][2 * dp], pf[0][kk], vb[0], vb[1]);
+          df_mma(o[0][2 * dp + 1], pf[0][kk], vb[2], vb[3]);
+          df_mma(o[1][2 * dp], pf[1][kk], vb[0], vb[1]);
+          df_mma(o[1][2 * dp + 1], pf[1][kk], vb[2], vb[3]);
         }
       }
     }
@@ -485,14 +514,15 @@ DL_EXPORT int dl_diff_attention_prefill(const void* q, int q_stride, const void*
   if (!dl::df_params(a, q, q_stride, cache, record, k_off, v_off, block_table, max_blocks, out, out_stride, n_heads, n_kv_heads,
                      dim, vdim, page_size, scale, softcap, lambda, out_scale, eps))
     return DL_ERR_UNSUPPORTED;
-  dim3 grid(n_tiles * (dl::DF_TILE / dl::DF_BM), n_heads);
+  dim3 grid(n_heads, n_tiles * (dl::DF_TILE / dl::DF_BM));
+  if (grid.y > 65535) return DL_ERR_UNSUPPORTED;
   if (vdim <= 32) return dl::df_launch<32, false>(a, grid, tiles, nullptr, nullptr, nullptr, 1, stream);
   if (vdim <= 64) return dl::df_launch<64, false>(a, grid, tiles, nullptr, nullptr, nullptr, 1, stream);
   return dl::df_launch<128, false>(a, grid, tiles, nullptr, nullptr, nullptr, 1, stream);
 }
 
 // Rows that bring one token each (rows 0 .. rows - 1 of q and out). n_split > 1 deals every row's keys over that
-// many blocks; scratch then needs rows * n_heads * n_split * 2 * (vdim + 2) floats.
+// many blocks (at most 32); scratch then needs rows * n_heads * n_split * 2 * (vdim + 2) floats.
 DL_EXPORT int dl_diff_attention_decode(const void* q, int q_stride, const void* cache, long long record, int k_off, int v_off,
                                        const int* block_table, int max_blocks, const int* positions, const int* row_slot,
                                        void* out, int out_stride, float* scratch, int rows, int n_heads, int n_kv_heads,
@@ -501,7 +531,7 @@ DL_EXPORT int dl_diff_attention_decode(const void* q, int q_stride, const void* 
   if (rows <= 0) return 0;
   dl::DiffParams a;
   if (!dl::df_params(a, q, q_stride, cache, record, k_off, v_off, block_table, max_blocks, out, out_stride, n_heads, n_kv_heads,
-                     dim, vdim, page_size, scale, softcap, lambda, out_scale, eps) || n_split < 1 || n_split > 65535 ||
+                     dim, vdim, page_size, scale, softcap, lambda, out_scale, eps) || n_split < 1 || n_split > 32 ||
       (n_split > 1 && scratch == nullptr))
     return DL_ERR_UNSUPPORTED;
   const int group = n_heads / n_kv_heads;

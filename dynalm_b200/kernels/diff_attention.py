@@ -15,8 +15,9 @@ from . import ops
 from .attention import QUERY_TILES, query_tiles
 from .device import sm_count
 
-MAX_SPLITS = 32
+MAX_SPLITS = 32           # the merge kernel holds one part per lane
 PART_MIN_KEYS = 256       # fewest keys of a part: four tiles, one 16-key group of each for every warp
+BLOCKS_PER_SM = 2         # blocks of the single-token kernel the split count aims for (three fit an SM at the widest sizes)
 
 
 def fast_applies(spec, q: torch.Tensor, records: torch.Tensor, page_size: int) -> bool:
@@ -26,13 +27,15 @@ def fast_applies(spec, q: torch.Tensor, records: torch.Tensor, page_size: int) -
 
 
 def split_count(rows: int, n_heads: int, n_kv_heads: int, span: int) -> int:
-    """Parts every single-token row's keys are dealt into, so that the grid about fills the GPU: the span is taken in
+    """Parts every single-token row's keys are dealt into, so that the grid about fills the GPU (a block walks its
+    tiles one after the other, so more and shorter blocks end sooner: 8 rows of 2,048 keys on 4 KV heads take 75 us in one
+    part, 35 us in five, 32 us in eight): the span is taken in
     powers of two (a growing context changes the launch shape only now and then) and a part keeps PART_MIN_KEYS keys."""
     bucket = PART_MIN_KEYS
     while bucket < span:
         bucket *= 2
     blocks = rows * n_kv_heads * -(-(n_heads // n_kv_heads) // 16)
-    want = -(-sm_count() // max(blocks, 1))
+    want = -(-BLOCKS_PER_SM * sm_count() // max(blocks, 1))
     return max(1, min(want, bucket // PART_MIN_KEYS, MAX_SPLITS))
 
 
