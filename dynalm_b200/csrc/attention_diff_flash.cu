@@ -139,8 +139,8 @@ __device__ __forceinline__ void df_finish_row(const float (&sum)[2], const float
 
 // tiles[i] = (request slot, first row of the step, rows, first position)   [prompt kernel]
 // positions / row_slot per row                                            [single-token kernel]
-template <int VDMAX, bool SINGLE>
-__global__ void __launch_bounds__(DF_THREADS)
+template <int VDMAX, bool SINGLE, int MAPS>
+__global__ void __launch_bounds__(DF_THREADS * (3 - MAPS), MAPS == 1 ? 2 : (VDMAX <= 64 ? 3 : 1))
 diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __restrict__ positions,
                   const int* __restrict__ row_slot, float* __restrict__ scratch, int n_split) {
   constexpr int QROWS = SINGLE ? 16 : DF_BM;       // rows of the Q tile in shared memory
@@ -152,7 +152,11 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
   bf16* Ks = Qs + QROWS * LDQ;                     // [2][DF_BN][LDQ]
   bf16* Vs = Ks + 2 * DF_BN * LDQ;                 // [2][DF_BN][LDV]
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // MAPS == 2: four warps, each with both maps of its 16 rows. MAPS == 1 (prompt portions only): eight warps, warps 0..3
+  // take map 1 and warps 4..7 map 2 of the same four groups of 16 rows: half the accumulators a thread, so that twice as
+  // many warps fit an SM and hide each other's latencies; the second map's output crosses shared memory at the end.
+  constexpr int THREADS = DF_THREADS * (3 - MAPS);
+  const int tid = threadIdx.x, lane = tid & 31, warp = (tid >> 5) & 3, my_map = MAPS == 1 ? tid >> 7 : 0;
   const int g = lane >> 2, t = lane & 3;
   const int group = a.n_heads / a.n_kv_heads;
   int req, row0, nrows, pos0, head0, kvh, nheads_here;
@@ -194,7 +198,7 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
   // Q tile -> shared (rows past the end are zero): a row of the tile is a token (prompt) or a head (single token)
   const int CHQ = 2 * dim / 8;
   const uint32_t qs_base = static_cast<uint32_t>(__cvta_generic_to_shared(Qs));
-  for (int c = tid; c < QROWS * CHQ; c += DF_THREADS) {
+  for (int c = tid; c < QROWS * CHQ; c += THREADS) {
     const int r = c / CHQ, ch = c % CHQ;
     const bool ok = SINGLE ? r < nheads_here : r < nrows;
     const int rr = ok ? r : 0;
@@ -207,9 +211,10 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
   const int CHV = vd / 8;
   const size_t k_at = static_cast<size_t>(a.k_off) + static_cast<size_t>(kvh) * 2 * dim;
   const size_t v_at = static_cast<size_t>(a.v_off) + static_cast<size_t>(kvh) * vd;
-  // Two threads copy one key's record: its page is looked up once per tile and thread, and the 16-byte pieces of the
-  // key's two maps and of its values go out without another dependent load in between.
-  const int kv_r = tid >> 1, kv_half = tid & 1;
+  // Two threads (four in a block of eight warps) copy one key's record: its page is looked up once per tile and thread,
+  // and the 16-byte pieces of the key's two maps and of its values go out without another dependent load in between.
+  constexpr int TPK = THREADS / DF_BN;
+  const int kv_r = tid / TPK, kv_half = tid % TPK;
   const uint32_t k_row = static_cast<uint32_t>(kv_r * LDQ * sizeof(bf16)), v_row = static_cast<uint32_t>(kv_r * LDV * sizeof(bf16));
   // the record of this thread's key of tile j (its number in the cache), -1 past the last key: looked up one
   // tile before its copies are issued, so that no copy waits for its page id
@@ -225,21 +230,21 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
     const bool ok = slot >= 0;
     const bf16* ksrc = a.cache + (ok ? rec : 0) + k_at;
     const bf16* vsrc = a.cache + (ok ? rec : 0) + v_at;
-    for (int ch = kv_half; ch < CHQ; ch += 2) df_cp16(k_stage + ch * 16, ksrc + ch * 8, ok);
-    for (int ch = kv_half; ch < CHV; ch += 2) df_cp16(v_stage + ch * 16, vsrc + ch * 8, ok);
+    for (int ch = kv_half; ch < CHQ; ch += TPK) df_cp16(k_stage + ch * 16, ksrc + ch * 8, ok);
+    for (int ch = kv_half; ch < CHV; ch += TPK) df_cp16(v_stage + ch * 16, vsrc + ch * 8, ok);
   };
   if (j_begin <= j_end) load_kv(find_record(j_begin), 0);
   df_commit();
   int rec_next = find_record(j_begin + 1);
 
-  float o[2][VDMAX / 8][4];
+  float o[MAPS][VDMAX / 8][4];
 #pragma unroll
-  for (int m = 0; m < 2; ++m)
+  for (int m = 0; m < MAPS; ++m)
 #pragma unroll
     for (int i = 0; i < VDMAX / 8; ++i) { o[m][i][0] = o[m][i][1] = o[m][i][2] = o[m][i][3] = 0.0f; }
-  float m_run[2][2], l_run[2][2];
+  float m_run[MAPS][2], l_run[MAPS][2];
 #pragma unroll
-  for (int m = 0; m < 2; ++m) { m_run[m][0] = m_run[m][1] = -INFINITY; l_run[m][0] = l_run[m][1] = 0.0f; }
+  for (int m = 0; m < MAPS; ++m) { m_run[m][0] = m_run[m][1] = -INFINITY; l_run[m][0] = l_run[m][1] = 0.0f; }
   // position of the lane's two rows (a single token: all rows are the one position)
   const int pos_a = SINGLE ? pos0 : pos0 + warp * 16 + g, pos_b = SINGLE ? pos0 : pos_a + 8;
   const int q_row = (SINGLE ? 0 : warp * 16) + (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -264,20 +269,21 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
     const bf16* vt = Vs + stage * DF_BN * LDV;
     const int key0 = j * DF_BN + kg0 * 16;
     const bool edge = key0 + NKG * 16 - 1 > (SINGLE ? pos0 : pos0 + warp * 16);
-    uint32_t pf[2][NKG][4];          // both maps' weights as bf16 A fragments
+    uint32_t pf[MAPS][NKG][4];       // the maps' weights as bf16 A fragments
 #pragma unroll
-    for (int m = 0; m < 2; ++m) {
+    for (int m = 0; m < MAPS; ++m) {
+      const int q_map = MAPS == 2 ? m : my_map;       // which map's slice of queries and keys
       float s[NKG * 2][4];
 #pragma unroll
       for (int i = 0; i < NKG * 2; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
       for (int ks = 0; ks < KS; ++ks) {
         uint32_t qf[4];
-        df_ldmatrix_x4(qf, Qs + q_row * LDQ + m * dim + ks * 16 + (lane >> 4) * 8);
+        df_ldmatrix_x4(qf, Qs + q_row * LDQ + q_map * dim + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
         for (int np = 0; np < NKG; ++np) {
           uint32_t kb[4];
           const int key = (kg0 + np) * 16 + (lane & 7) + (lane >> 4) * 8;
-          df_ldmatrix_x4(kb, kt + key * LDQ + m * dim + ks * 16 + ((lane >> 3) & 1) * 8);
+          df_ldmatrix_x4(kb, kt + key * LDQ + q_map * dim + ks * 16 + ((lane >> 3) & 1) * 8);
           df_mma(s[2 * np], qf, kb[0], kb[1]);
           df_mma(s[2 * np + 1], qf, kb[2], kb[3]);
         }
@@ -342,10 +348,11 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
           uint32_t vb[4];
           const int key = (kg0 + kk) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
           df_ldmatrix_x4_trans(vb, vt + key * LDV + dp * 16 + (lane >> 4) * 8);
-          df_mma(o[0][2 * dp], pf[0][kk], vb[0], vb[1]);
-          df_mma(o[0][2 * dp + 1], pf[0][kk], vb[2], vb[3]);
-          df_mma(o[1][2 * dp], pf[1][kk], vb[0], vb[1]);
-          df_mma(o[1][2 * dp + 1], pf[1][kk], vb[2], vb[3]);
+#pragma unroll
+          for (int m = 0; m < MAPS; ++m) {
+            df_mma(o[m][2 * dp], pf[m][kk], vb[0], vb[1]);
+            df_mma(o[m][2 * dp + 1], pf[m][kk], vb[2], vb[3]);
+          }
         }
       }
     }
@@ -354,21 +361,44 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
   df_wait<0>();
 
   const float lambda = a.lambda[0];
-  if (!SINGLE) {
+  if constexpr (!SINGLE) {
     // a row's values lie in the four lanes of its quad: difference, sum of squares over the quad, scale, store
-    float inv[2][2];
+    float inv[MAPS][2];
 #pragma unroll
-    for (int m = 0; m < 2; ++m)
+    for (int m = 0; m < MAPS; ++m)
 #pragma unroll
       for (int h = 0; h < 2; ++h) inv[m][h] = l_run[m][h] > 0.0f ? 1.0f / l_run[m][h] : 0.0f;
+    float* second = reinterpret_cast<float*>(Ks);     // [DF_BM][vd]: the second map's output on its way to the first map's warps
+    if (MAPS == 1) {
+      __syncthreads();                                // nobody reads the key tiles any more (and no copy is in flight)
+      if (my_map == 1) {
+#pragma unroll
+        for (int i = 0; i < VDMAX / 8; ++i) {
+          if (i * 8 < vd) {
+            float* dst = second + (warp * 16 + g) * vd + i * 8 + 2 * t;
+            *reinterpret_cast<float2*>(dst) = make_float2(o[0][i][0] * inv[0][0], o[0][i][1] * inv[0][0]);
+            *reinterpret_cast<float2*>(dst + 8 * vd) = make_float2(o[0][i][2] * inv[0][1], o[0][i][3] * inv[0][1]);
+          }
+        }
+      }
+      __syncthreads();
+      if (my_map == 1) return;
+    }
     float ss[2] = {0.0f, 0.0f};
 #pragma unroll
     for (int i = 0; i < VDMAX / 8; ++i) {
       if (i * 8 < vd) {
+        float other[4];
+        if (MAPS == 1) {
+          const float* src = second + (warp * 16 + g) * vd + i * 8 + 2 * t;
+          const float2 lo = *reinterpret_cast<const float2*>(src), hi = *reinterpret_cast<const float2*>(src + 8 * vd);
+          other[0] = lo.x; other[1] = lo.y; other[2] = hi.x; other[3] = hi.y;
+        }
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int h = e >> 1;
-          const float v = o[0][i][e] * inv[0][h] - lambda * (o[1][i][e] * inv[1][h]);
+          const float a2 = MAPS == 1 ? other[e] : o[MAPS - 1][i][e] * inv[MAPS - 1][h];
+          const float v = o[0][i][e] * inv[0][h] - lambda * a2;
           o[0][i][e] = v;
           ss[h] = fmaf(v, v, ss[h]);
         }
@@ -394,8 +424,7 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
       }
     }
     return;
-  }
-
+  } else {
   // Single token: every warp leaves its part [16 rows][2 maps][(max, sum, acc[vd])] in shared memory (over the key
   // and value tiles, which nobody reads any more), then warp w merges the four parts of rows w, w + 4, ...
   float* parts = reinterpret_cast<float*>(smem_raw);
@@ -442,6 +471,7 @@ diff_flash_kernel(DiffParams a, const int4* __restrict__ tiles, const int* __res
       }
     }
   }
+  }
 }
 
 // Finishes the rows whose keys were dealt over n_split blocks: one warp per (row, head).
@@ -468,18 +498,18 @@ inline size_t df_smem_bytes(bool single, int dim, int vd) {
   return tiles > merge ? tiles : merge;
 }
 
-template <int VDMAX, bool SINGLE>
+template <int VDMAX, bool SINGLE, int MAPS>
 int df_launch(const DiffParams& a, dim3 grid, const int* tiles, const int* positions, const int* row_slot, float* scratch,
               int n_split, cudaStream_t stream) {
   const size_t smem = df_smem_bytes(SINGLE, a.dim, a.vd);
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(diff_flash_kernel<VDMAX, SINGLE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(diff_flash_kernel<VDMAX, SINGLE, MAPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = smem;
   }
-  diff_flash_kernel<VDMAX, SINGLE><<<grid, DF_THREADS, smem, stream>>>(a, reinterpret_cast<const int4*>(tiles), positions,
+  diff_flash_kernel<VDMAX, SINGLE, MAPS><<<grid, DF_THREADS * (3 - MAPS), smem, stream>>>(a, reinterpret_cast<const int4*>(tiles), positions,
                                                                       row_slot, scratch, n_split);
   return launch_status();
 }
@@ -516,9 +546,19 @@ DL_EXPORT int dl_diff_attention_prefill(const void* q, int q_stride, const void*
     return DL_ERR_UNSUPPORTED;
   dim3 grid(n_heads, n_tiles * (dl::DF_TILE / dl::DF_BM));
   if (grid.y > 65535) return DL_ERR_UNSUPPORTED;
-  if (vdim <= 32) return dl::df_launch<32, false>(a, grid, tiles, nullptr, nullptr, nullptr, 1, stream);
-  if (vdim <= 64) return dl::df_launch<64, false>(a, grid, tiles, nullptr, nullptr, nullptr, 1, stream);
-  return dl::df_launch<128, false>(a, grid, tiles, nullptr, nullptr, nullptr, 1, stream);
+  // The maps are dealt over two sets of warps (half the registers a thread, twice the warps an SM): measured on B200 at
+  // 2,048 tokens, us a layer, both maps in one warp / dealt: 16 heads of 64 + 64 with values of 128: 169 / 147; values of
+  // 64: 148 / 124; maps and values of 128: 288 / 242; 32 heads of 32 with values of 64: 194 / 189.
+  // DYNALM_DIFF_SPLIT_MAPS=0 keeps both maps in one warp (for measurements).
+  static int forced = -2;
+  if (forced == -2) { const char* e = getenv("DYNALM_DIFF_SPLIT_MAPS"); forced = e ? atoi(e) : -1; }
+  const bool split_maps = forced != 0;
+  if (vdim <= 32) return split_maps ? dl::df_launch<32, false, 1>(a, grid, tiles, nullptr, nullptr, nullptr, 1, stream)
+                                    : dl::df_launch<32, false, 2>(a, grid, tiles, nullptr, nullptr, nullptr, 1, stream);
+  if (vdim <= 64) return split_maps ? dl::df_launch<64, false, 1>(a, grid, tiles, nullptr, nullptr, nullptr, 1, stream)
+                                    : dl::df_launch<64, false, 2>(a, grid, tiles, nullptr, nullptr, nullptr, 1, stream);
+  return split_maps ? dl::df_launch<128, false, 1>(a, grid, tiles, nullptr, nullptr, nullptr, 1, stream)
+                    : dl::df_launch<128, false, 2>(a, grid, tiles, nullptr, nullptr, nullptr, 1, stream);
 }
 
 // Rows that bring one token each (rows 0 .. rows - 1 of q and out). n_split > 1 deals every row's keys over that
@@ -538,9 +578,9 @@ DL_EXPORT int dl_diff_attention_decode(const void* q, int q_stride, const void* 
   dim3 grid(rows, n_kv_heads * ((group + 15) / 16), n_split);
   if (grid.y > 65535) return DL_ERR_UNSUPPORTED;
   int rc;
-  if (vdim <= 32) rc = dl::df_launch<32, true>(a, grid, nullptr, positions, row_slot, scratch, n_split, stream);
-  else if (vdim <= 64) rc = dl::df_launch<64, true>(a, grid, nullptr, positions, row_slot, scratch, n_split, stream);
-  else rc = dl::df_launch<128, true>(a, grid, nullptr, positions, row_slot, scratch, n_split, stream);
+  if (vdim <= 32) rc = dl::df_launch<32, true, 2>(a, grid, nullptr, positions, row_slot, scratch, n_split, stream);
+  else if (vdim <= 64) rc = dl::df_launch<64, true, 2>(a, grid, nullptr, positions, row_slot, scratch, n_split, stream);
+  else rc = dl::df_launch<128, true, 2>(a, grid, nullptr, positions, row_slot, scratch, n_split, stream);
   if (rc != 0 || n_split == 1) return rc;
   dim3 mgrid(rows, (n_heads + dl::DF_THREADS / 32 - 1) / (dl::DF_THREADS / 32));
 #define DL_MERGE(V)                                                                                                     \

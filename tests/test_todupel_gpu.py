@@ -123,7 +123,8 @@ def _attention_case(heads, groups, dim, vdim, n_keys, page, dtype, seed, scale, 
     return rng, kw, vw, keys, values
 
 
-ATTENTION_SHAPES = [(4, 2, 16, 32), (6, 2, 48, 16), (2, 2, 64, 64), (5, 1, 20, 36), (8, 2, 128, 128), (4, 1, 32, 128)]
+ATTENTION_SHAPES = [(4, 2, 16, 32), (6, 2, 48, 16), (2, 2, 64, 64), (5, 1, 20, 36), (8, 2, 128, 128), (4, 1, 32, 128),
+                    (20, 1, 16, 16)]       # the last: more heads on a KV head than one tile of the single-token kernel holds
 
 
 def _run_attention(kind, q, cache, kw, table, pos_t, slot_t, heads, groups, dim, vdim, page, scale, cap, lam, out_scale, eps):
