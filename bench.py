@@ -341,8 +341,8 @@ ARCH_VOCAB = 32000
 
 def arch_pair(name):
     width, layers, heads, kv, dim, inter = ARCH_SIZES[name]
-    mixer = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": 2 * dim, "scale": dim ** -0.5, "softcap": 50.0, "diff": 0.5,
-             "q_temp": {"coef": 0.3, "every": 128}}
+    mixer = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": 2 * dim, "scale": dim ** -0.5, "softcap": 30.0, "diff": 0.4,
+             "q_temp": {"coef": 0.2, "every": 256}}
     todupel = {"architecture": "Todupel", "vocab": ARCH_VOCAB, "width": width, "norm": {"eps": 1e-5},
                "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": {"kind": "dense", "ff": inter * 3 // 2}}
                           for _ in range(layers)]}

@@ -32,7 +32,7 @@ def test_config_reads_every_size_per_layer():
     assert [r.cache_of for r in plan.order] == [None, None, 0]
     s = plan.layers[2].mixer
     assert (s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, s.scale, s.softcap, s.lambda_init, s.temp_every, s.own_kv) == \
-        (6, 2, 48, 16, 0.15, 50.0, 0.5, 3, False)
+        (6, 2, 48, 16, 0.15, 40.0, 0.55, 3, False)
     assert "ffn" not in plan.layers[1].parts and plan.layers[0].ffn.inner == 112
 
 

@@ -31,7 +31,7 @@ T_A = {"architecture": "Todupel", "vocab": 300, "width": 96, "norm": {"eps": 1e-
 T_B = {"architecture": "Todupel", "vocab": 257, "width": 80, "norm": {"eps": 3e-5}, "layers": [
     _layer(_mixer(6, 2, 48, 16, 0.2, 3.0, 0.6, (0.7, 5)), 112),
     _layer(_mixer(3, 1, 32, 48, 0.3, 20.0, 0.2, (0.1, 13)), None),
-    _layer(_mixer(6, 2, 48, 16, 0.15, 50.0, 0.5, (1.0, 3), kv_from=0), 64),
+    _layer(_mixer(6, 2, 48, 16, 0.15, 40.0, 0.55, (1.0, 3), kv_from=0), 64),
 ]}
 
 # One head per key/value head, maps and values of one size (64: the widest tile paths), no cap and no temperature
