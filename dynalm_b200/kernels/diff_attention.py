@@ -17,7 +17,10 @@ from .device import sm_count
 
 MAX_SPLITS = 32           # the merge kernel holds one part per lane
 PART_MIN_KEYS = 256       # fewest keys of a part: four tiles, one 16-key group of each for every warp
-BLOCKS_PER_SM = 2         # blocks of the single-token kernel the split count aims for (three fit an SM at the widest sizes)
+TILE_KEYS = 64
+BLOCKS_PER_SM = 3         # blocks of the single-token kernel that share an SM (registers allow three at every size)
+BLOCK_OVERHEAD_TILES = 2  # what a block costs besides its tiles (first loads, the merge of its warps), in tiles
+MERGE_TILES = 2           # what the kernel that merges the parts costs, in tiles
 
 
 def fast_applies(spec, q: torch.Tensor, records: torch.Tensor, page_size: int) -> bool:
@@ -26,17 +29,24 @@ def fast_applies(spec, q: torch.Tensor, records: torch.Tensor, page_size: int) -
             and records.shape[-1] % 8 == 0 and (spec.num_kv_heads * 2 * spec.head_dim) % 8 == 0)
 
 
-def split_count(rows: int, n_heads: int, n_kv_heads: int, span: int) -> int:
-    """Parts every single-token row's keys are dealt into, so that the grid about fills the GPU (a block walks its
-    tiles one after the other, so more and shorter blocks end sooner: 8 rows of 2,048 keys on 4 KV heads take 75 us in one
-    part, 35 us in five, 32 us in eight): the span is taken in
-    powers of two (a growing context changes the launch shape only now and then) and a part keeps PART_MIN_KEYS keys."""
+def split_count(rows: int, n_heads: int, n_kv_heads: int, span: int, sms: int = 0) -> int:
+    """Parts every single-token row's keys are dealt into. A block walks its tiles one after the other (1.8 us a tile
+    measured), so the kernel takes (rounds of blocks over the GPU) x (tiles of a block + what a block costs besides),
+    plus the merge when there are parts: the count with the least of that, every part keeping PART_MIN_KEYS keys.
+    Measured on B200, 8 rows of 2,048 keys on 4 KV heads: 75 us in one part, 35 us in five, 32 us in eight. The span
+    is taken in powers of two, so that a growing context changes the launch shape (and the CUDA graph) only now and then."""
     bucket = PART_MIN_KEYS
     while bucket < span:
         bucket *= 2
     blocks = rows * n_kv_heads * -(-(n_heads // n_kv_heads) // 16)
-    want = -(-BLOCKS_PER_SM * sm_count() // max(blocks, 1))
-    return max(1, min(want, bucket // PART_MIN_KEYS, MAX_SPLITS))
+    slots = BLOCKS_PER_SM * (sms or sm_count())
+    tiles = bucket // TILE_KEYS
+    best, least = 1, None
+    for parts in range(1, min(MAX_SPLITS, bucket // PART_MIN_KEYS) + 1):
+        cost = -(-blocks * parts // slots) * (-(-tiles // parts) + BLOCK_OVERHEAD_TILES) + (MERGE_TILES if parts > 1 else 0)
+        if least is None or cost < least:
+            best, least = parts, cost
+    return best
 
 
 def step_plans() -> list:

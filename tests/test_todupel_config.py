@@ -107,3 +107,19 @@ def test_plain_mechanisms_by_hand():
     o = plain.diff_combine(np.array([[2.0, 0.0]]), np.array([[0.0, 2.0]]), 1.0, 0.25, 0.0)
     assert np.allclose(o, np.array([[1.0, -1.0]]) * 0.75)
     assert np.allclose(plain.relu2_mlp(np.array([[1.0, -2.0]]), np.eye(2), np.array([[1.0, 1.0]])), [[1.0]])
+
+
+def test_split_count_of_the_single_token_kernel():
+    """Every part keeps 256 keys, there are at most 32, few rows are dealt finer than many, and the count depends on the
+    span only through its power of two (a growing context keeps its launch shape)."""
+    from dynalm_b200.kernels.diff_attention import split_count
+    for rows in (1, 3, 8, 64, 200):
+        for span in (1, 17, 255, 256, 257, 2000, 5000, 70000):
+            n = split_count(rows, 16, 4, span, sms=148)
+            bucket = 256
+            while bucket < span:
+                bucket *= 2
+            assert 1 <= n <= 32 and n * 256 <= max(bucket, 256)
+            assert n == split_count(rows, 16, 4, bucket, sms=148)
+    assert split_count(1, 16, 4, 4000, sms=148) >= split_count(64, 16, 4, 4000, sms=148) >= split_count(500, 16, 4, 4000, sms=148) == 1
+    assert split_count(8, 16, 4, 100, sms=148) == 1
