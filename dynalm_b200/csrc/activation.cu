@@ -1,6 +1,6 @@
 // Gated activation: out[t, j] = silu(gu[t, j]) * gu[t, inner + j], gu = [gate | up] side by side.
 // silu(x) = x * sigmoid(x) (dynacore/cpu/cpu_device.cpp:117-123; CpuDevice::act_mul :1912-1929).
-// The math is fp32 whatever the storage type. Also here: the squared ReLU of an ungated feed-forward.
+// The math is fp32 whatever the storage type. Also here: the squared ReLU and the tanh form of GELU of an ungated feed-forward.
 #include "common.cuh"
 
 namespace dl {
@@ -58,7 +58,51 @@ __global__ void relu2_vec_kernel(const T* __restrict__ x, T* __restrict__ out, s
   reinterpret_cast<Vec16*>(out)[i] = pack<T>(f);
 }
 
+// GELU in its tanh form: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), the activation of an ungated feed-forward.
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void gelu_tanh_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  out[i] = from_float<T>(gelu_tanh_f(to_float(x[i])));
+}
+
+// 16 bytes per access; n counts vectors.
+template <typename T>
+__global__ void gelu_tanh_vec_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n) {
+  constexpr int V = PerVec<T>::n;
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float f[V];
+  unpack<T>(reinterpret_cast<const Vec16*>(x)[i], f);
+#pragma unroll
+  for (int j = 0; j < V; ++j) f[j] = gelu_tanh_f(f[j]);
+  reinterpret_cast<Vec16*>(out)[i] = pack<T>(f);
+}
+
 }  // namespace dl
+
+// out[i] = gelu_tanh(x[i]) over n contiguous elements (out may be x).
+DL_EXPORT int dl_gelu_tanh(int dtype, const void* x, void* out, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (dtype != 0 && dtype != 1) return DL_ERR_UNSUPPORTED;
+  const int threads = 256;
+  const int vec = dtype == 0 ? 4 : 8;
+  if (n % vec == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    const size_t nv = static_cast<size_t>(n / vec);
+    const unsigned blocks = static_cast<unsigned>((nv + threads - 1) / threads);
+    if (dtype == 0) dl::gelu_tanh_vec_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(x), static_cast<float*>(out), nv);
+    else dl::gelu_tanh_vec_kernel<dl::bf16><<<blocks, threads, 0, stream>>>(static_cast<const dl::bf16*>(x), static_cast<dl::bf16*>(out), nv);
+    return dl::launch_status();
+  }
+  const unsigned blocks = static_cast<unsigned>((static_cast<size_t>(n) + threads - 1) / threads);
+  if (dtype == 0) dl::gelu_tanh_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(x), static_cast<float*>(out), static_cast<size_t>(n));
+  else dl::gelu_tanh_kernel<dl::bf16><<<blocks, threads, 0, stream>>>(static_cast<const dl::bf16*>(x), static_cast<dl::bf16*>(out), static_cast<size_t>(n));
+  return dl::launch_status();
+}
 
 // out[i] = max(x[i], 0)^2 over n contiguous elements (out may be x).
 DL_EXPORT int dl_relu2(int dtype, const void* x, void* out, long long n, cudaStream_t stream) {

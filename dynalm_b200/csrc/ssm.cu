@@ -1,0 +1,286 @@
+// A state-space mixer's kernels: short causal convolution, the recurrence of every head, and the gated norm of
+// its output. One projection of the layer's input gives a row [z: H*P | x: H*P | B: G*N | C: G*N | dt: H]
+// (H heads of P channels, N state rows, G groups of heads that share B and C).
+//
+//   u    = silu(conv(x | B | C))        per channel, K taps, the last tap is the current token's, zeros before the start
+//   dt_h = softplus(dt_h + bias_h)
+//   S_h  = exp(-exp(a_h) dt_h) S_h + dt_h B x_h^T        (S_h is N x P, float32, carried from token to token)
+//   y_h  = S_h^T C + D_h x_h
+//   out  = norm_parts(y * silu(z)) * w                   (each of `parts` equal pieces by its own root mean square)
+//
+// What a request keeps between steps is one float32 row of a state array: H*N*P numbers of S, then the last K - 1
+// inputs of the convolution, [K - 1][C], oldest first. A step may bring any number of consecutive tokens of a
+// request; every kernel finds a row's request, position and slot in the step's arrays. Decays, step sizes, the
+// state and the sums over it are float32 whatever the storage type of the projection.
+#include "common.cuh"
+
+namespace dl {
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+
+// ---- convolution --------------------------------------------------------------------------------------------
+// One thread per (row, channel). The K - 1 inputs in front of a row come from the rows above it while those
+// belong to the same step, and from the request's kept inputs otherwise.
+template <typename T>
+__global__ void ssm_conv_kernel(const T* __restrict__ proj, int proj_stride, int col0, int channels,
+                                const float* __restrict__ taps, const float* __restrict__ bias, int K,
+                                const float* __restrict__ state, size_t state_stride, size_t keep_off,
+                                const int* __restrict__ positions, const int* __restrict__ row_request,
+                                const int* __restrict__ row_slot, const int* __restrict__ pos_start,
+                                T* __restrict__ out, int rows) {
+  const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<size_t>(rows) * channels) return;
+  const int row = static_cast<int>(idx / channels), ch = static_cast<int>(idx % channels);
+  const int pos = positions[row];
+  const int first = pos_start[ck_request(row_request[row])];      // the position of the request's first row in this step
+  const float* kept = state + static_cast<size_t>(ck_request(row_slot[row])) * state_stride + keep_off;
+  float acc = bias ? bias[ch] : 0.0f;
+  for (int k = K - 1; k >= 0; --k) {                               // oldest input first
+    const int p = pos - k;
+    float v;
+    if (p >= first) v = to_float(proj[static_cast<size_t>(row - k) * proj_stride + col0 + ch]);
+    else v = kept[static_cast<size_t>(K - 1 - (first - p)) * channels + ch];
+    acc = fmaf(taps[static_cast<size_t>(ch) * K + (K - 1 - k)], v, acc);
+  }
+  out[idx] = from_float<T>(silu_f(acc));
+}
+
+// After the convolution of a step: the last K - 1 inputs of every request, oldest first. One thread per (request,
+// channel); entries are written in ascending order, and entry j only ever needs an older entry at a higher index.
+template <typename T>
+__global__ void ssm_conv_keep_kernel(const T* __restrict__ proj, int proj_stride, int col0, int channels, int K,
+                                     float* __restrict__ state, size_t state_stride, size_t keep_off,
+                                     const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                                     int requests) {
+  const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<size_t>(requests) * channels) return;
+  const int r = static_cast<int>(idx / channels), ch = static_cast<int>(idx % channels);
+  const int r0 = q_start[r], n = q_start[r + 1] - r0;
+  float* kept = state + static_cast<size_t>(ck_request(state_slots[r])) * state_stride + keep_off;
+  for (int j = 0; j < K - 1; ++j) {
+    const int rel = n - (K - 1) + j;                               // which of the step's rows entry j is, if any
+    kept[static_cast<size_t>(j) * channels + ch] =
+        rel >= 0 ? to_float(proj[static_cast<size_t>(r0 + rel) * proj_stride + col0 + ch])
+                 : kept[static_cast<size_t>(j + n) * channels + ch];
+  }
+}
+
+// ---- recurrence ---------------------------------------------------------------------------------------------
+// Block = (request, head, slice of PV channels). Thread (p, j) keeps rows n = j, j + NS, j + 2 NS, ... of column p
+// of S in registers (at most NR of them). The request's tokens of this step are walked in tiles of TT: a tile's B, C,
+// x, step sizes and decays go to shared memory, every thread then runs the tile's tokens over its registers and
+// leaves its share of every y in shared memory, and the shares of a channel are added in a fixed order.
+constexpr int SCAN_TT = 8;
+
+template <typename T, int NR>
+__global__ void ssm_scan_kernel(const T* __restrict__ u, int u_stride,            // [rows, H*P + 2*G*N] after the convolution
+                                const T* __restrict__ proj, int proj_stride, int dt_col,   // dt of head h at proj[row, dt_col + h]
+                                const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                const float* __restrict__ d_skip, float* __restrict__ state, size_t state_stride,
+                                const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                                float* __restrict__ y, int H, int P, int N, int G, int PV, int NS) {
+  extern __shared__ float sm[];
+  float* sB = sm;                               // [TT][N]
+  float* sC = sB + SCAN_TT * N;                 // [TT][N]
+  float* sX = sC + SCAN_TT * N;                 // [TT][PV]
+  float* sY = sX + SCAN_TT * PV;                // [TT][NS][PV]
+  float* sDt = sY + SCAN_TT * NS * PV;          // [TT] step sizes, then [TT] decays
+  float* sDa = sDt + SCAN_TT;
+  const int r = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * PV;
+  const int tid = threadIdx.x, pl = tid % PV, j = tid / PV;
+  const int p = p0 + pl;
+  const bool live = p < P;
+  const int g = h / (H / G);
+  const int inner = H * P;
+  const int r0 = q_start[r], n_tok = q_start[r + 1] - r0;
+  float* S = state + static_cast<size_t>(ck_request(state_slots[r])) * state_stride + static_cast<size_t>(h) * N * P;
+  const float rate = expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
+  float s[NR];
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    const int n = j + i * NS;
+    s[i] = (live && n < N) ? S[static_cast<size_t>(n) * P + p] : 0.0f;
+  }
+  for (int t0 = 0; t0 < n_tok; t0 += SCAN_TT) {
+    const int tt = min(SCAN_TT, n_tok - t0);
+    __syncthreads();                            // the tile before has been read
+    for (int i = tid; i < tt * N; i += blockDim.x) {
+      const int t = i / N, n = i % N;
+      const T* ur = u + static_cast<size_t>(r0 + t0 + t) * u_stride + inner + g * N + n;
+      sB[i] = to_float(ur[0]);
+      sC[i] = to_float(ur[G * N]);
+    }
+    for (int i = tid; i < tt * PV; i += blockDim.x) {
+      const int t = i / PV, q = p0 + i % PV;
+      sX[i] = q < P ? to_float(u[static_cast<size_t>(r0 + t0 + t) * u_stride + h * P + q]) : 0.0f;
+    }
+    if (tid < tt) {
+      const float raw = to_float(proj[static_cast<size_t>(r0 + t0 + tid) * proj_stride + dt_col + h]);
+      const float dt = softplus_f(raw + bias);
+      sDt[tid] = dt;
+      sDa[tid] = expf(-rate * dt);
+    }
+    __syncthreads();
+    for (int t = 0; t < tt; ++t) {
+      const float dt = sDt[t], da = sDa[t];
+      const float xv = sX[t * PV + pl] * dt;
+      const float* b = sB + t * N;
+      const float* c = sC + t * N;
+      float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < NR; i += 2) {
+        const int n0 = j + i * NS, n1 = j + (i + 1) * NS;
+        if (n0 < N) {
+          s[i] = fmaf(da, s[i], b[n0] * xv);
+          acc0 = fmaf(s[i], c[n0], acc0);
+        }
+        if (i + 1 < NR && n1 < N) {
+          s[i + 1] = fmaf(da, s[i + 1], b[n1] * xv);
+          acc1 = fmaf(s[i + 1], c[n1], acc1);
+        }
+      }
+      sY[(t * NS + j) * PV + pl] = acc0 + acc1;
+    }
+    __syncthreads();
+    for (int i = tid; i < tt * PV; i += blockDim.x) {
+      const int t = i / PV, q = i % PV;
+      if (p0 + q < P) {
+        float sum = 0.0f;
+        for (int k = 0; k < NS; ++k) sum += sY[(t * NS + k) * PV + q];
+        y[static_cast<size_t>(r0 + t0 + t) * inner + h * P + p0 + q] = fmaf(skip, sX[t * PV + q], sum);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    const int n = j + i * NS;
+    if (live && n < N) S[static_cast<size_t>(n) * P + p] = s[i];
+  }
+}
+
+// ---- gated norm -----------------------------------------------------------------------------------------------
+// Block = (row, part). v = y * silu(z) over the part's channels, out = v / sqrt(mean(v^2) + eps) * w.
+template <typename T>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, int z_stride,
+                                        const float* __restrict__ w, float eps, T* __restrict__ out, int inner,
+                                        int part_len) {
+  __shared__ float red[33];
+  const int row = blockIdx.x, c0 = blockIdx.y * part_len;
+  const float* yr = y + static_cast<size_t>(row) * inner + c0;
+  const T* zr = z + static_cast<size_t>(row) * z_stride + c0;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < part_len; i += blockDim.x) {
+    const float v = yr[i] * silu_f(to_float(zr[i]));
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(part_len) + eps);
+  T* orow = out + static_cast<size_t>(row) * inner + c0;
+  for (int i = threadIdx.x; i < part_len; i += blockDim.x) {
+    const float v = yr[i] * silu_f(to_float(zr[i]));
+    orow[i] = from_float<T>(v * inv * w[c0 + i]);
+  }
+}
+
+}  // namespace dl
+
+// out[row, ch] = silu(bias[ch] + sum_k taps[ch, k] * input(row's position - (K - 1 - k), ch)), the inputs being
+// columns col0 .. col0 + channels of proj. state: [slots, state_stride] float32, a slot's kept inputs at keep_off.
+DL_EXPORT int dl_ssm_conv(int dtype, const void* proj, int proj_stride, int col0, int channels, const float* taps,
+                          const float* bias, int K, const float* state, long long state_stride, long long keep_off,
+                          const int* positions, const int* row_request, const int* row_slot, const int* pos_start,
+                          void* out, int rows, cudaStream_t stream) {
+  if (rows <= 0 || channels <= 0) return 0;
+  if (K <= 0) return DL_ERR_UNSUPPORTED;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((static_cast<size_t>(rows) * channels + threads - 1) / threads);
+#define DL_LAUNCH(T)                                                                                                    \
+  dl::ssm_conv_kernel<T><<<blocks, threads, 0, stream>>>(static_cast<const T*>(proj), proj_stride, col0, channels, taps, \
+                                                         bias, K, state, static_cast<size_t>(state_stride),             \
+                                                         static_cast<size_t>(keep_off), positions, row_request,         \
+                                                         row_slot, pos_start, static_cast<T*>(out), rows)
+  if (dtype == 0) DL_LAUNCH(float);
+  else if (dtype == 1) DL_LAUNCH(dl::bf16);
+  else return DL_ERR_UNSUPPORTED;
+#undef DL_LAUNCH
+  return dl::launch_status();
+}
+
+DL_EXPORT int dl_ssm_conv_keep(int dtype, const void* proj, int proj_stride, int col0, int channels, int K, float* state,
+                               long long state_stride, long long keep_off, const int* q_start, const int* state_slots,
+                               int requests, cudaStream_t stream) {
+  if (requests <= 0 || channels <= 0 || K <= 1) return 0;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((static_cast<size_t>(requests) * channels + threads - 1) / threads);
+  if (dtype == 0)
+    dl::ssm_conv_keep_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(proj), proj_stride, col0, channels, K, state,
+                                                                    static_cast<size_t>(state_stride), static_cast<size_t>(keep_off),
+                                                                    q_start, state_slots, requests);
+  else if (dtype == 1)
+    dl::ssm_conv_keep_kernel<dl::bf16><<<blocks, threads, 0, stream>>>(static_cast<const dl::bf16*>(proj), proj_stride, col0, channels, K,
+                                                                       state, static_cast<size_t>(state_stride),
+                                                                       static_cast<size_t>(keep_off), q_start, state_slots, requests);
+  else return DL_ERR_UNSUPPORTED;
+  return dl::launch_status();
+}
+
+// u: the convolution's output [rows, H*P + 2*G*N]; proj: the projection (for dt); y: float32 [rows, H*P].
+DL_EXPORT int dl_ssm_scan(int dtype, const void* u, int u_stride, const void* proj, int proj_stride, int dt_col,
+                          const float* dt_bias, const float* a_log, const float* d_skip, float* state,
+                          long long state_stride, const int* q_start, const int* state_slots, float* y, int requests, int H,
+                          int P, int N, int G, cudaStream_t stream) {
+  if (requests <= 0) return 0;
+  if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G != 0 || H > 65535) return DL_ERR_UNSUPPORTED;
+  // rows of S per thread: 32 at most; NS threads share a channel
+  const int NR = N <= 8 ? 8 : (N <= 64 ? 16 : 32);
+  const int NS = (N + NR - 1) / NR;
+  if (NS > 32) return DL_ERR_UNSUPPORTED;                          // N up to 1,024
+  int PV = P < 32 ? P : 32;
+  while (PV * 2 <= P && PV * 2 * NS <= 256) PV *= 2;
+  const int slices = (P + PV - 1) / PV;
+  if (slices > 65535) return DL_ERR_UNSUPPORTED;
+  const int threads = PV * NS;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(dl::SCAN_TT) * (2 * N + PV + NS * PV) + 2 * dl::SCAN_TT);
+  if (smem > 200 * 1024) return DL_ERR_UNSUPPORTED;
+  dim3 grid(requests, H, slices);
+#define DL_LAUNCH(T, R)                                                                                               \
+  do {                                                                                                                \
+    if (smem > 48 * 1024)                                                                                             \
+      cudaFuncSetAttribute(dl::ssm_scan_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    dl::ssm_scan_kernel<T, R><<<grid, threads, smem, stream>>>(static_cast<const T*>(u), u_stride, static_cast<const T*>(proj), \
+                                                               proj_stride, dt_col, dt_bias, a_log, d_skip, state,    \
+                                                               static_cast<size_t>(state_stride), q_start, state_slots, \
+                                                               y, H, P, N, G, PV, NS);                                \
+  } while (0)
+#define DL_PICK(T)                   \
+  do {                               \
+    if (NR == 8) DL_LAUNCH(T, 8);    \
+    else if (NR == 16) DL_LAUNCH(T, 16); \
+    else DL_LAUNCH(T, 32);           \
+  } while (0)
+  if (dtype == 0) DL_PICK(float);
+  else if (dtype == 1) DL_PICK(dl::bf16);
+  else return DL_ERR_UNSUPPORTED;
+#undef DL_PICK
+#undef DL_LAUNCH
+  return dl::launch_status();
+}
+
+// y: float32 [rows, inner]; z: rows of z_stride elements (the gate's columns first); out: [rows, inner].
+DL_EXPORT int dl_gated_group_norm(int dtype, const float* y, const void* z, int z_stride, const float* w, float eps,
+                                  void* out, int rows, int inner, int parts, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (inner <= 0 || parts <= 0 || inner % parts != 0 || parts > 65535) return DL_ERR_UNSUPPORTED;
+  const int part_len = inner / parts;
+  const int threads = part_len >= 1024 ? 256 : (part_len >= 256 ? 128 : 64);
+  dim3 grid(rows, parts);
+  if (dtype == 0)
+    dl::gated_group_norm_kernel<float><<<grid, threads, 0, stream>>>(y, static_cast<const float*>(z), z_stride, w, eps,
+                                                                     static_cast<float*>(out), inner, part_len);
+  else if (dtype == 1)
+    dl::gated_group_norm_kernel<dl::bf16><<<grid, threads, 0, stream>>>(y, static_cast<const dl::bf16*>(z), z_stride, w, eps,
+                                                                        static_cast<dl::bf16*>(out), inner, part_len);
+  else return DL_ERR_UNSUPPORTED;
+  return dl::launch_status();
+}

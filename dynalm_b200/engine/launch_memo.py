@@ -14,7 +14,7 @@ What makes this safe:
   calls, and depends only on the step, the block's inputs and the part's own tensors. A part defined elsewhere
   (a test's toy mixer) does not say so and always runs through its own `forward`;
 * a list is reused only by a layer with the same block class and spec, the same state of the residual stream on
-  entry (what is pending, where, at what scale), and tensors of the same shapes, dtypes, strides and 16-byte
+  entry (what is pending, where, at what scale, whether a copy of it in the compute dtype exists), and tensors of the same shapes, dtypes, strides and 16-byte
   alignment in the same order;
 * every argument that points into one of the recorded layer's tensors is moved to the same offset of the other
   layer's tensor (a library product is written down with its tensors, and the layer's own tensor among them is
@@ -74,9 +74,9 @@ class _Layout:
 
 
 class _Record:
-    __slots__ = ("calls", "own", "library", "pending", "pending_scale", "pending2")
+    __slots__ = ("calls", "own", "library", "pending", "pending_scale", "pending2", "as_input")
 
-    def __init__(self, calls, pending, pending_scale, pending2=None):
+    def __init__(self, calls, pending, pending_scale, pending2=None, as_input=None):
         # [(function, arguments, ((argument index, tensor index, offset or None for the tensor itself), ...))]
         self.calls = calls
         self.library = sum(1 for f, _, _ in calls if f is ops.library_mm_again)
@@ -84,6 +84,7 @@ class _Record:
         self.pending = pending
         self.pending_scale = pending_scale
         self.pending2 = pending2
+        self.as_input = as_input
 
 
 def _patches(calls, layout: _Layout):
@@ -135,7 +136,8 @@ class LayerLaunchMemo:
         pending, second = stream.pending, stream.pending2
         key = (self.kinds[index], owns_cache, stream.x.data_ptr(), stream.pending_scale,
                None if pending is None else (pending.data_ptr(), tuple(pending.shape), pending.dtype),
-               None if second is None else (second.data_ptr(), tuple(second.shape), second.dtype), layout.signature)
+               None if second is None else (second.data_ptr(), tuple(second.shape), second.dtype),
+               None if stream.as_input is None else stream.as_input.data_ptr(), layout.signature)
         if key in self.records:
             record = self.records[key]
             if record is None:
@@ -154,6 +156,7 @@ class LayerLaunchMemo:
             global REPLAYED_LAYERS
             REPLAYED_LAYERS += 1
             stream.pending, stream.pending_scale, stream.pending2 = record.pending, record.pending_scale, record.pending2
+            stream.as_input = record.as_input
             return stream
         with ops.Recording() as recording:
             stream = block.forward(stream, ctx, cache, owns_cache)
@@ -161,5 +164,5 @@ class LayerLaunchMemo:
             self.records[key] = None             # some work was not written down: this kind runs through its parts
         else:
             self.records[key] = _Record(_patches(recording.calls, layout), stream.pending, stream.pending_scale,
-                                        stream.pending2)
+                                        stream.pending2, stream.as_input)
         return stream

@@ -174,6 +174,20 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, runtime, inner: int)
     return act
 
 
+def linear_act(x: torch.Tensor, w_up: torch.Tensor, runtime, inner: int, activation: str) -> torch.Tensor:
+    """act(x W^T), the first half of an ungated feed-forward, for the activations the kernels have: "relu2" sits in
+    the product's epilogue where it can (linear_relu2); "gelu_tanh" follows the product as a kernel of its own."""
+    if activation == "relu2":
+        return linear_relu2(x, w_up, runtime, inner)
+    act = runtime.buffer("ffn_act", (x.shape[0], inner))
+    linear(x, w_up, act)
+    if activation == "gelu_tanh":
+        ops.gelu_tanh(act, act)
+    else:
+        raise ValueError(f"no kernel for activation '{activation}'")
+    return act
+
+
 def linear_relu2(x: torch.Tensor, w_up: torch.Tensor, runtime, inner: int) -> torch.Tensor:
     """max(x W^T, 0)^2, the first half of an ungated feed-forward: the activation sits in the product's epilogue
     wherever one of this package's bfloat16 kernels runs the product, else the product is followed by the

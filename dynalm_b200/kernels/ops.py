@@ -28,7 +28,21 @@ _SIGNATURES = {
         "dl_residual_add": [_I, _P, _P, _F, _L, _I, _L, _P],
         "dl_rmsnorm_pair": [_I, _P, _P, _I, _I, _L, _P, _I, _I, _L, _P, _P, _F, _P, _P, _P, _I, _I, _I, _P],
     },
-    "activation": {"dl_silu_mul": [_I, _P, _P, _I, _I, _P], "dl_relu2": [_I, _P, _P, _L, _P]},
+    "activation": {"dl_silu_mul": [_I, _P, _P, _I, _I, _P], "dl_relu2": [_I, _P, _P, _L, _P],
+                   "dl_gelu_tanh": [_I, _P, _P, _L, _P]},
+    "norm_after_sum": {
+        "dl_norm_after_sum": [_I, _I, _P, _P, _I, _L, _P, _F, _P, _F, _P, _I, _I, _P],
+        "dl_cast_rows": [_I, _P, _P, _L, _P]},
+    "ssm": {
+        "dl_ssm_conv": [_I, _P, _I, _I, _I, _P, _P, _I, _P, _L, _L, _P, _P, _P, _P, _P, _I, _P],
+        "dl_ssm_conv_keep": [_I, _P, _I, _I, _I, _I, _P, _L, _L, _P, _P, _I, _P],
+        "dl_ssm_scan": [_I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "dl_gated_group_norm": [_I, _P, _P, _I, _P, _F, _P, _I, _I, _I, _P]},
+    "latent_attention": {
+        "dl_latent_prep": [_I, _P, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _I, _P, _P, _I, _P],
+        "dl_rotate_pairs": [_I, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P],
+        "dl_head_linear": [_I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _P],
+        "dl_latent_attention": [_I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]},
     "qk_norm_cache": {
         "dl_qk_norm_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _L, _I, _I, _P, _P, _F, _F, _I, _I, _I, _I, _I, _I,
                                    _I, _I, _P]},
@@ -487,6 +501,216 @@ def relu2(x: torch.Tensor, out: torch.Tensor) -> None:
     if x.shape != out.shape or x.dtype != out.dtype or not x.is_contiguous() or not out.is_contiguous():
         raise InvalidArgument("relu2: x and out contiguous, of one shape and dtype")
     _check(_fn("activation", "dl_relu2")(dtype_code(x.dtype), _p(x), _p(out), x.numel(), _stream()), "relu2")
+
+
+def gelu_tanh(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) elementwise (out may be x); both contiguous, of one dtype."""
+    _cuda(x, out)
+    if x.shape != out.shape or x.dtype != out.dtype or not x.is_contiguous() or not out.is_contiguous():
+        raise InvalidArgument("gelu_tanh: x and out contiguous, of one shape and dtype")
+    _check(_fn("activation", "dl_gelu_tanh")(dtype_code(x.dtype), _p(x), _p(out), x.numel(), _stream()), "gelu_tanh")
+
+
+def norm_after_sum(x: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float, alpha: float = 1.0,
+                   delta_scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> None:
+    """x <- rmsnorm(alpha * x + delta_scale * delta) * weight, row by row, and out <- the same rows in out's dtype.
+
+    x: float32 [n, width], replaced; delta: [n, width] of either dtype or [parts, n, width] partial sums added in
+    order; delta_scale: float32 [width] or None; weight: float32 [width]; out: [n, width] or None. See
+    csrc/norm_after_sum.cu."""
+    _cuda(x, delta, weight, delta_scale, out)
+    rows, width = x.shape
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or not x.is_contiguous() or weight.numel() != width:
+        raise InvalidArgument("norm_after_sum: x and weight float32, x contiguous, widths equal")
+    if delta_scale is not None and (delta_scale.dtype != torch.float32 or delta_scale.numel() != width):
+        raise InvalidArgument("norm_after_sum: the scale of delta must be float32 [width]")
+    if out is not None and (out.shape != x.shape or not out.is_contiguous()):
+        raise InvalidArgument("norm_after_sum: out must be contiguous and of x's shape")
+    parts, part_stride = _delta_parts(delta, width, "norm_after_sum")
+    if delta.shape[-2] < rows:
+        raise InvalidArgument("norm_after_sum: delta has fewer rows than x")
+    od = dtype_code(out.dtype) if out is not None else dtype_code(delta.dtype)
+    _take_ahead()
+    _check(_fn("norm_after_sum", "dl_norm_after_sum")(
+        od, dtype_code(delta.dtype), _p(x), _p(delta), parts, part_stride, _p(delta_scale), alpha, _p(weight), eps,
+        _p(out), rows, width, _stream()), "norm_after_sum")
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (float32) in out's dtype; both contiguous and of one shape."""
+    _cuda(x, out)
+    if x.dtype != torch.float32 or x.shape != out.shape or not x.is_contiguous() or not out.is_contiguous():
+        raise InvalidArgument("cast_rows: x float32, x and out contiguous and of one shape")
+    _check(_fn("norm_after_sum", "dl_cast_rows")(dtype_code(out.dtype), _p(x), _p(out), x.numel(), _stream()), "cast_rows")
+
+
+def ssm_conv(proj: torch.Tensor, col0: int, channels: int, taps: torch.Tensor, bias: Optional[torch.Tensor],
+             state: torch.Tensor, keep_off: int, positions: torch.Tensor, row_request: torch.Tensor,
+             row_slot: torch.Tensor, pos_start: torch.Tensor, out: torch.Tensor) -> None:
+    """out[row, ch] = silu(bias[ch] + sum_k taps[ch, k] * u(position - (K - 1 - k), ch)), u = columns col0 .. col0 +
+    channels of proj; inputs in front of a request's first row of the step come from its kept inputs, state[slot,
+    keep_off + j * channels + ch] (oldest first). taps: float32 [channels, K]; state: float32 [slots, n]. See
+    csrc/ssm.cu."""
+    _cuda(proj, taps, bias, state, positions, row_request, row_slot, pos_start, out)
+    _rows_contiguous(proj, "proj")
+    rows = proj.shape[0]
+    K = taps.shape[1]
+    if taps.dtype != torch.float32 or not taps.is_contiguous() or taps.shape[0] != channels \
+            or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != channels)):
+        raise InvalidArgument("ssm_conv: taps float32 [channels, K] and bias float32 [channels]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or keep_off + (K - 1) * channels > state.shape[1]:
+        raise InvalidArgument("ssm_conv: state float32 [slots, n] with room for the kept inputs")
+    if out.dtype != proj.dtype or out.shape != (rows, channels) or not out.is_contiguous() or col0 + channels > proj.shape[1]:
+        raise InvalidArgument("ssm_conv: out contiguous [rows, channels] of proj's dtype; the channels lie inside proj")
+    check_limits("ssm", requests=state.shape[0], rows=rows)
+    _check(_fn("ssm", "dl_ssm_conv")(dtype_code(proj.dtype), _p(proj), proj.stride(0), col0, channels, _p(taps), _p(bias), K,
+                                      _p(state), state.stride(0), keep_off, _p(positions), _p(row_request), _p(row_slot),
+                                      _p(pos_start), _p(out), rows, _stream()), "ssm_conv")
+
+
+def ssm_conv_keep(proj: torch.Tensor, col0: int, channels: int, K: int, state: torch.Tensor, keep_off: int,
+                  q_start: torch.Tensor, state_slots: torch.Tensor, requests: int) -> None:
+    """After a step's convolution: every request's last K - 1 inputs into its kept inputs (those it brought in this
+    step, and the newest of the old ones where it brought fewer)."""
+    _cuda(proj, state, q_start, state_slots)
+    _rows_contiguous(proj, "proj")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or keep_off + (K - 1) * channels > state.shape[1]:
+        raise InvalidArgument("ssm_conv_keep: state float32 [slots, n] with room for the kept inputs")
+    check_limits("ssm", requests=state.shape[0], rows=proj.shape[0])
+    _check(_fn("ssm", "dl_ssm_conv_keep")(dtype_code(proj.dtype), _p(proj), proj.stride(0), col0, channels, K, _p(state),
+                                           state.stride(0), keep_off, _p(q_start), _p(state_slots), requests, _stream()),
+           "ssm_conv_keep")
+
+
+def ssm_scan(u: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+             d_skip: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, state_slots: torch.Tensor, y: torch.Tensor,
+             requests: int, heads: int, head_dim: int, n_state: int, groups: int) -> None:
+    """The recurrence of every head over every request's rows of the step, from and into state[slot, :H*N*P] ([H, N,
+    P]). u: [rows, H*P + 2*G*N] after the convolution (x | B | C); proj[row, dt_col + h]: the raw step size; y:
+    float32 [rows, H*P]. See csrc/ssm.cu."""
+    _cuda(u, proj, dt_bias, a_log, d_skip, state, q_start, state_slots, y)
+    _rows_contiguous(u, "u")
+    _rows_contiguous(proj, "proj")
+    inner = heads * head_dim
+    if u.dtype != proj.dtype or u.shape[1] != inner + 2 * groups * n_state or dt_col + heads > proj.shape[1]:
+        raise InvalidArgument("ssm_scan: u is [rows, H*P + 2*G*N] of proj's dtype and proj holds H step sizes from dt_col")
+    if any(t.dtype != torch.float32 or t.numel() != heads for t in (dt_bias, a_log, d_skip)):
+        raise InvalidArgument("ssm_scan: dt_bias, a_log and d are float32 [heads]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < inner * n_state:
+        raise InvalidArgument("ssm_scan: state float32 [slots, >= H*N*P]")
+    if y.dtype != torch.float32 or not y.is_contiguous() or y.shape != (u.shape[0], inner):
+        raise InvalidArgument("ssm_scan: y float32 contiguous [rows, H*P]")
+    check_limits("ssm", requests=state.shape[0], rows=u.shape[0])
+    _check(_fn("ssm", "dl_ssm_scan")(dtype_code(u.dtype), _p(u), u.stride(0), _p(proj), proj.stride(0), dt_col, _p(dt_bias),
+                                      _p(a_log), _p(d_skip), _p(state), state.stride(0), _p(q_start), _p(state_slots),
+                                      _p(y), requests, heads, head_dim, n_state, groups, _stream()), "ssm_scan")
+
+
+def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, parts: int,
+                     out: torch.Tensor) -> None:
+    """out = norm_parts(y * silu(z)) * weight: each of `parts` equal pieces of a row by its own root mean square. y:
+    float32 [rows, inner]; z: rows whose first `inner` columns are the gate; out: [rows, inner] of z's dtype."""
+    _cuda(y, z, weight, out)
+    _rows_contiguous(z, "z")
+    rows, inner = y.shape
+    if y.dtype != torch.float32 or not y.is_contiguous() or z.shape[1] < inner or weight.dtype != torch.float32 \
+            or weight.numel() != inner or out.shape != y.shape or out.dtype != z.dtype or not out.is_contiguous():
+        raise InvalidArgument("gated_group_norm: y float32 [rows, inner], z at least as wide, weight float32 [inner], out like y in z's dtype")
+    if parts <= 0 or inner % parts:
+        raise InvalidArgument(f"gated_group_norm: {inner} channels do not divide into {parts} parts")
+    _check(_fn("ssm", "dl_gated_group_norm")(dtype_code(z.dtype), _p(y), _p(z), z.stride(0), _p(weight), eps, _p(out),
+                                              rows, inner, parts, _stream()), "gated_group_norm")
+
+
+def latent_prep(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, rot: int, q_weight: torch.Tensor,
+                kv_weight: torch.Tensor, eps: float, freq: Optional[torch.Tensor], positions: torch.Tensor,
+                row_slot: torch.Tensor, block_table: torch.Tensor, cache: torch.Tensor, page_size: int,
+                cq: torch.Tensor) -> None:
+    """Per row of proj = [query latent | latent | key part | ...]: cq = rmsnorm(query latent) * q_weight, and the row's
+    record [rmsnorm(latent) * kv_weight | key part with its first `rot` numbers turned by the position] into the paged
+    cache [pages, page_size, kv_rank + rot_dim]. freq: float64 [rot / 2]. See csrc/latent_attention.cu."""
+    _cuda(proj, q_weight, kv_weight, freq, positions, row_slot, block_table, cache, cq)
+    _rows_contiguous(proj, "proj")
+    rows = proj.shape[0]
+    if proj.shape[1] < q_rank + kv_rank + rot_dim:
+        raise InvalidArgument("latent_prep: proj is narrower than its three pieces")
+    if q_weight.dtype != torch.float32 or q_weight.numel() != q_rank or kv_weight.dtype != torch.float32 or kv_weight.numel() != kv_rank:
+        raise InvalidArgument("latent_prep: norm weights float32 [q_rank] and [kv_rank]")
+    if rot and (freq is None or freq.dtype != torch.float64 or freq.numel() != rot // 2):
+        raise InvalidArgument("latent_prep: freq float64 [rot / 2]")
+    if cache.dtype != proj.dtype or not cache.is_contiguous() or cache.dim() != 3 or cache.shape[1] != page_size \
+            or cache.shape[2] != kv_rank + rot_dim:
+        raise InvalidArgument("latent_prep: the cache must be contiguous [pages, page_size, kv_rank + rot_dim] of proj's dtype")
+    if cq.dtype != proj.dtype or cq.shape != (rows, q_rank) or not cq.is_contiguous():
+        raise InvalidArgument("latent_prep: cq contiguous [rows, q_rank] of proj's dtype")
+    if block_table.dtype != torch.int32 or block_table.stride(-1) != 1:
+        raise InvalidArgument("latent_prep: block_table must be int32 rows")
+    check_limits("latent_attention", pages=cache.shape[0], requests=block_table.shape[0], rows=rows)
+    _check(_fn("latent_attention", "dl_latent_prep")(
+        dtype_code(proj.dtype), _p(proj), proj.stride(0), q_rank, kv_rank, rot_dim, rot, _p(q_weight), _p(kv_weight), eps,
+        _p(freq), _p(positions), _p(row_slot), _p(block_table), block_table.stride(0), page_size, _p(cq), _p(cache), rows,
+        _stream()), "latent_prep")
+
+
+def rotate_pairs(q: torch.Tensor, head_in: int, in_off: int, out: torch.Tensor, head_out: int, out_off: int, r: int,
+                 rot: int, freq: Optional[torch.Tensor], positions: torch.Tensor, heads: int) -> None:
+    """out[row, h * head_out + out_off + i] = q[row, h * head_in + in_off + i] for i < r, the first `rot` of them
+    turned in interleaved pairs (2i, 2i + 1) by position * freq[i]."""
+    _cuda(q, out, freq, positions)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    if q.dtype != out.dtype or q.shape[0] != out.shape[0] or (heads - 1) * head_in + in_off + r > q.shape[1] \
+            or (heads - 1) * head_out + out_off + r > out.shape[1]:
+        raise InvalidArgument("rotate_pairs: q and out of one dtype and row count, the heads' pieces inside them")
+    if rot and (freq is None or freq.dtype != torch.float64 or freq.numel() != rot // 2):
+        raise InvalidArgument("rotate_pairs: freq float64 [rot / 2]")
+    _check(_fn("latent_attention", "dl_rotate_pairs")(
+        dtype_code(q.dtype), _p(q), q.stride(0), head_in, in_off, _p(out), out.stride(0), head_out, out_off, r, rot,
+        _p(freq), _p(positions), q.shape[0], heads, _stream()), "rotate_pairs")
+
+
+def head_linear(x: torch.Tensor, head_in: int, n_in: int, w: torch.Tensor, out: torch.Tensor, head_out: int,
+                gate: Optional[torch.Tensor] = None, gate_head: int = 0) -> None:
+    """out[row, h * head_out + j] = sum_i x[row, h * head_in + i] * w[h, i, j] for every head h (a block-diagonal
+    product), times sigmoid(gate[row, h * gate_head + j]) when a gate is given. w: contiguous [H, n_in, n_out]."""
+    _cuda(x, w, out, gate)
+    _rows_contiguous(x, "x")
+    _rows_contiguous(out, "out")
+    if w.dim() != 3 or not w.is_contiguous() or w.shape[1] != n_in or w.dtype != x.dtype or out.dtype != x.dtype:
+        raise InvalidArgument("head_linear: w contiguous [H, n_in, n_out]; x, w and out of one dtype")
+    H, n_out = w.shape[0], w.shape[2]
+    if (H - 1) * head_in + n_in > x.shape[1] or (H - 1) * head_out + n_out > out.shape[1] or out.shape[0] != x.shape[0]:
+        raise InvalidArgument("head_linear: the heads' pieces do not fit x or out")
+    if gate is not None:
+        _rows_contiguous(gate, "gate")
+        if gate.dtype != x.dtype or gate.shape[0] < x.shape[0] or (H - 1) * gate_head + n_out > gate.shape[1]:
+            raise InvalidArgument("head_linear: the gate's pieces do not fit")
+    _check(_fn("latent_attention", "dl_head_linear")(
+        dtype_code(x.dtype), _p(x), x.stride(0), head_in, n_in, _p(w), n_out, _p(out), out.stride(0), head_out, _p(gate),
+        gate.stride(0) if gate is not None else 0, gate_head, x.shape[0], H, _stream()), "head_linear")
+
+
+def latent_attention(qw: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor,
+                     row_slot: torch.Tensor, sink: Optional[torch.Tensor], out: torch.Tensor, heads: int, kv_rank: int,
+                     rot_dim: int, page_size: int, scale: float, window: int) -> None:
+    """Every row's wide queries [H, kv_rank + rot_dim] over the records of its request's window; out [rows, H,
+    kv_rank] = softmax-weighted sum of the records' latents, the denominator also holding exp(sink[h]) when sinks are
+    given. The plain kernel; see csrc/latent_attention.cu."""
+    _cuda(qw, cache, block_table, positions, row_slot, sink, out)
+    _rows_contiguous(qw, "qw")
+    _rows_contiguous(out, "out")
+    rw = kv_rank + rot_dim
+    if qw.dtype != cache.dtype or out.dtype != qw.dtype or qw.shape[1] < heads * rw or out.shape[1] < heads * kv_rank:
+        raise InvalidArgument("latent_attention: qw, cache and out of one dtype; qw [rows, H*(R+r)], out [rows, H*R]")
+    if cache.dim() != 3 or cache.shape[1] != page_size or cache.shape[2] != rw or not cache.is_contiguous():
+        raise InvalidArgument("latent_attention: the cache is not contiguous [pages, page_size, kv_rank + rot_dim]")
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != heads):
+        raise InvalidArgument("latent_attention: sinks float32 [heads]")
+    check_limits("latent_attention", pages=cache.shape[0], requests=block_table.shape[0], rows=qw.shape[0])
+    _check(_fn("latent_attention", "dl_latent_attention")(
+        dtype_code(qw.dtype), _p(qw), qw.stride(0), _p(cache), _p(block_table), block_table.stride(0), _p(positions),
+        _p(row_slot), _p(sink), _p(out), out.stride(0), qw.shape[0], heads, kv_rank, rot_dim, page_size, scale, window,
+        _stream()), "latent_attention")
 
 
 def qk_norm_cache_write(qkv: torch.Tensor, positions: torch.Tensor, row_slot: torch.Tensor,

@@ -4,6 +4,8 @@
 (dynalm/src/model/transformer.cpp:602-697). "parallel": x += mixer(norm1(x)) + ffn(norm2(x)), both
 parts fed from the same x. The residual stream is float32; the sum of a part's output into it is
 fused into the norm that follows, so a block leaves its last output (the parallel one: both) pending.
+"post_norm": x <- norm1(a x + mixer(x)); x <- norm2(a x + ffn(x)): the sublayers read the stream itself and each
+norm closes its own sum, so nothing is left pending and the stream is always a normed row.
 """
 
 from __future__ import annotations
@@ -26,6 +28,7 @@ class ResidualStream:
     pending: Optional[torch.Tensor] = None
     pending_scale: float = 1.0
     pending2: Optional[torch.Tensor] = None
+    as_input: Optional[torch.Tensor] = None      # x in the compute dtype, when the part that wrote x last also left that
 
     def flush(self) -> torch.Tensor:
         if self.pending is not None:
@@ -102,6 +105,7 @@ class PreNormBlock(Block):
         self.ffn_norm.forward(stream.x, h, delta=a, delta_scale=self.scale)
         f = self.ffn.forward(h, ctx)
         stream.pending, stream.pending_scale = f, self.scale
+        stream.as_input = None
         return stream
 
 
@@ -130,4 +134,38 @@ class ParallelBlock(Block):
         a = self.mixer.forward(h1, ctx, cache, owns_cache)
         f = self.ffn.forward(h2, ctx) if self.has_ffn else None
         stream.pending, stream.pending_scale, stream.pending2 = a, 1.0, f
+        stream.as_input = None
+        return stream
+
+
+@register_block("post_norm")
+class PostNormBlock(Block):
+    """parts: mixer, mixer_norm, and optionally ffn + ffn_norm, the norms of a kind that closes a sum ("rms_after_sum":
+    they carry the weight alpha of the stream and the per-channel scale of the sublayer's result). x <-
+    mixer_norm(alpha x + mixer(x)), then x <- ffn_norm(alpha x + ffn(x)). A sublayer's matrix products read x in the
+    compute dtype; the norm kernel writes that copy beside the float32 stream (on the 32-bit path the stream itself is
+    read), and the first layer of a model makes it from the embedding."""
+
+    def __init__(self, spec, store, runtime):
+        super().__init__(spec, store, runtime)
+        self.has_ffn = "ffn" in spec.parts
+
+    def forward(self, stream: ResidualStream, ctx, cache, owns_cache: bool) -> ResidualStream:
+        rows, width = stream.x.shape
+        stream.flush()                             # (an arrangement that leaves its outputs pending may stand in front)
+        narrow = self.rt.dtype != torch.float32
+        h = stream.as_input
+        if not narrow:
+            h = stream.x
+        elif h is None:
+            h = self.rt.buffer("stream_copy", (rows, width))
+            ops.cast_rows(stream.x, h)
+        a = self.mixer.forward(h, ctx, cache, owns_cache)
+        if narrow:
+            h = self.rt.buffer("stream_copy", (rows, width))
+        self.mixer_norm.forward(stream.x, h if narrow else None, a)
+        if self.has_ffn:
+            f = self.ffn.forward(h, ctx)
+            self.ffn_norm.forward(stream.x, h if narrow else None, f)
+        stream.as_input = h if narrow else None
         return stream

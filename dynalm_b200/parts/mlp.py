@@ -1,6 +1,6 @@
 """Gated feed-forward: down(act(gate x) * up x), the "gated_mlp" kind
 (dynalm/src/model/transformer.cpp:671-693). Gate and up run as one product against [Wg; Wu].
-Ungated feed-forward: down(act(up x)), the "mlp" kind, act the squared ReLU."""
+Ungated feed-forward: down(act(up x)), the "mlp" kind, act the squared ReLU or the tanh form of GELU."""
 
 from __future__ import annotations
 
@@ -10,7 +10,7 @@ import torch
 
 from ..errors import Unsupported
 from ..kernels import ops
-from ..kernels.gemm import linear_partial, linear_relu2, linear_swiglu
+from ..kernels.gemm import linear_act, linear_partial, linear_swiglu
 from .base import TensorDecl, register_feed_forward
 
 
@@ -49,7 +49,8 @@ class GatedMLP:
 
 @register_feed_forward("mlp")
 class DenseMLP:
-    """down(act(up x)) without a gate (parameters inner, activation: "relu2" = max(z, 0)^2)."""
+    """down(act(up x)) without a gate (parameters inner, activation: "relu2" = max(z, 0)^2, "gelu_tanh" =
+    0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
 
     replay_safe = True     # all device work goes through the recorded launches of kernels/ops.py (engine/launch_memo.py)
     graph_safe = True      # launches depend on row counts only
@@ -62,8 +63,9 @@ class DenseMLP:
         }
 
     def __init__(self, spec, tensors: Dict[str, torch.Tensor], runtime):
-        if spec.get("activation", "relu2") != "relu2":
-            raise Unsupported(f"mlp: activation '{spec.get('activation')}' has no kernel (relu2 does)")
+        self.activation = spec.get("activation", "relu2")
+        if self.activation not in ("relu2", "gelu_tanh"):
+            raise Unsupported(f"mlp: activation '{self.activation}' has no kernel (relu2 and gelu_tanh do)")
         self.spec = spec
         self.rt = runtime
         self.w_up = tensors["up"]
@@ -76,5 +78,5 @@ class DenseMLP:
         s, rt = self.spec, self.rt
         if x.shape[0] <= ops.SKINNY_FAST_ROWS:
             ops.stream_ahead(self.w_down)              # taken by the up product, read by the product after it
-        act = linear_relu2(x, self.w_up, rt, s.inner)
+        act = linear_act(x, self.w_up, rt, s.inner, self.activation)
         return linear_partial(act, self.w_down, rt, "ffn_out")

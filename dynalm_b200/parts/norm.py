@@ -1,4 +1,5 @@
-"""RMSNorm over the float32 residual stream (CpuDevice::rms_norm, dynacore/cpu/cpu_device.cpp:1179-1205)."""
+"""RMSNorm over the float32 residual stream (CpuDevice::rms_norm, dynacore/cpu/cpu_device.cpp:1179-1205), in front of a
+sublayer ("rms") or after the sum that a sublayer's result enters ("rms_after_sum")."""
 
 from __future__ import annotations
 
@@ -39,3 +40,30 @@ class RMSNorm:
         other's weight."""
         ops.rmsnorm_pair(residual, self.weight, out, other.weight if other is not None else None, other_out, self.eps,
                          delta_a=delta_a, delta_b=delta_b, rows=rows)
+
+
+@register_norm("rms_after_sum")
+class RMSNormAfterSum:
+    """x <- rmsnorm(alpha * x + delta_scale * delta) * weight: the norm of a layer that norms what it has just summed.
+    `alpha` (a parameter, default 1) weighs the stream against the sublayer's result; `delta_scale` is a per-channel
+    scale of that result, there when the model has its tensor. The stream itself becomes the normed row."""
+
+    replay_safe = True     # all device work goes through the recorded launches of kernels/ops.py (engine/launch_memo.py)
+    graph_safe = True      # launches depend on row counts only
+
+    @staticmethod
+    def declare(spec) -> Dict[str, TensorDecl]:
+        return {"weight": TensorDecl((spec.width,), role="vector", init="around_one"),
+                "delta_scale": TensorDecl((spec.width,), role="vector", required=False, init="around_one")}
+
+    def __init__(self, spec, tensors: Dict[str, torch.Tensor], runtime):
+        self.spec = spec
+        self.weight = tensors["weight"]
+        self.delta_scale = tensors.get("delta_scale")
+        self.eps = float(spec.eps)
+        self.alpha = float(spec.get("alpha", 1.0))
+
+    def forward(self, residual: torch.Tensor, out: Optional[torch.Tensor], delta: torch.Tensor) -> None:
+        """residual (float32, in place) <- the normed sum; out (compute dtype, or None) <- a copy for the products of
+        the next sublayer. delta: the sublayer's result, [n, width] or split-K partial sums [parts, n, width]."""
+        ops.norm_after_sum(residual, delta, self.weight, self.eps, self.alpha, self.delta_scale, out)

@@ -5,6 +5,10 @@ position scale (linear scaling), as CpuDevice::rope (dynacore/cpu/cpu_device.cpp
 frequencies are made here in 32-bit floats exactly as the reference makes them,
 `pow(base, -2 i / rot) / factor_i`; the rotation itself happens inside the fused kernel
 (csrc/rope_cache.cu), which asks this part for `table()`.
+"rotary_interleaved": rotary embedding in the interleaved layout: numbers 2i and 2i + 1 of the first `rotary_dim`
+of a vector form a pair that turns by position * theta^(-2i / rotary_dim). The frequencies are kept in double
+precision and the kernels form the angle in double precision (csrc/latent_attention.cu), so the rotation is exact to
+float32 at any position; the mixer that uses it asks for `frequencies`.
 "none": no position encoding.
 
 A further kind implements `table()` returning None and `apply(q, k, positions)` rotating its views in
@@ -59,6 +63,23 @@ class RotaryEncoding:
             ops.rope_angles(ctx.positions, self.inv_freq, self.pos_scale, ctx.num_tokens, got)
             ctx.extras[key] = got
         return got
+
+
+@register_position("rotary_interleaved")
+class InterleavedRotaryEncoding:
+    replay_safe = True     # it launches nothing itself
+    interleaved = True
+
+    def __init__(self, spec, runtime):
+        if spec.rotary_dim <= 0 or spec.rotary_dim > spec.head_dim or spec.rotary_dim % 2:
+            raise Unsupported(f"rotary_dim {spec.rotary_dim} invalid for a rotated part of {spec.head_dim} numbers")
+        i = np.arange(spec.rotary_dim // 2, dtype=np.float64)
+        self.spec = spec
+        self.rotary_dim = spec.rotary_dim
+        self.frequencies = torch.from_numpy(np.power(float(spec.theta), -2.0 * i / spec.rotary_dim)).to(runtime.device)
+
+    def table(self):
+        return None
 
 
 @register_position("none")
