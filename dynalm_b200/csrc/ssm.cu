@@ -115,11 +115,11 @@ __global__ void ssm_scan_kernel(const T* __restrict__ u, int u_stride,          
       const int t = i / PV, q = p0 + i % PV;
       sX[i] = q < P ? to_float(u[static_cast<size_t>(r0 + t0 + t) * u_stride + h * P + q]) : 0.0f;
     }
-    if (tid < tt) {
-      const float raw = to_float(proj[static_cast<size_t>(r0 + t0 + tid) * proj_stride + dt_col + h]);
+    for (int t = tid; t < tt; t += blockDim.x) {
+      const float raw = to_float(proj[static_cast<size_t>(r0 + t0 + t) * proj_stride + dt_col + h]);
       const float dt = softplus_f(raw + bias);
-      sDt[tid] = dt;
-      sDa[tid] = expf(-rate * dt);
+      sDt[t] = dt;
+      sDa[t] = expf(-rate * dt);
     }
     __syncthreads();
     for (int t = 0; t < tt; ++t) {
