@@ -14,8 +14,8 @@ leaves room for while the measurement grows them), and a prefill of 8,192 tokens
 of the roofline; last, the continuous-batching workloads of the 3B and 8B shapes (tokens/s over the whole run,
 median time to the first token, decode-only step), a 32,768-token prompt brought in portions of 512, and the
 end-to-end decode again with requests that draw their tokens (temperature, top-k, top-p, a penalty). `--workload serve3b | serve8b` runs one of those alone and
-prints its full record; `--workload todupel` measures the Todupel design beside the Llama shape of equal size at three
-sizes (`todupel-kernels`: the device time of every kernel of both). Prints one JSON line.
+prints its full record; `--workload todupel` (`rematar`) measures that design beside the Llama shape of equal size at three
+sizes (`todupel-kernels`, `rematar-kernels`: the device time of every kernel of both). Prints one JSON line.
 """
 
 import argparse
@@ -353,7 +353,36 @@ def arch_pair(name):
     return todupel, llama
 
 
-def arch_compare(args, kernels: bool):
+# --workload rematar: the Rematar design (state-space layers and latent attention in post-norm blocks) beside the
+# Llama shape of equal width, depth and feed-forward weights: the ungated feed-forward is 1.5 times as wide as the gated
+# one. The mixers are what the designs differ in; the record carries both weight counts.
+REMATAR_SIZES = {
+    # name: (width, layer kinds, (ssd heads, channels, state, groups, taps, normed parts),
+    #        (heads, dim, rot_dim, vdim, q_rank, kv_rank, window), llama (heads, kv_heads, head_dim, intermediate))
+    "w2048_n128": (2048, "sass", (64, 64, 128, 8, 4, 8), (16, 128, 64, 128, 768, 512, 1024), (16, 4, 128, 8192)),
+    "w4096_n128": (4096, "sa", (128, 64, 128, 8, 4, 8), (32, 128, 64, 128, 1536, 512, 2048), (32, 8, 128, 14336)),
+    "w2048_n64": (2048, "sass", (32, 128, 64, 1, 4, 1), (16, 64, 32, 64, 512, 256, 512), (32, 8, 64, 8192)),
+}
+
+
+def rematar_pair(name):
+    width, kinds, s, a, l = REMATAR_SIZES[name]
+    ssd = {"heads": s[0], "vdim": s[1], "state": s[2], "groups": s[3], "conv": s[4], "norm_groups": s[5]}
+    lat = {"heads": a[0], "dim": a[1], "rot_dim": a[2], "vdim": a[3], "q_rank": a[4], "kv_rank": a[5],
+           "scale": (a[1] + a[2]) ** -0.5, "rot": {"base": 10000.0, "dims": a[2]}, "mask": {"size": a[6]}}
+    mlp = {"kind": "dense", "ff": l[3] * 3 // 2}
+    rematar = {"architecture": "Rematar", "vocab": ARCH_VOCAB, "width": width, "norm": {"eps": 1e-5}, "postln_alpha": 2.0,
+               "embedding": {"scale": 8.0},
+               "layers": [{"type": "mamba2" if k == "s" else "latent_attention", "mixer": dict(ssd if k == "s" else lat),
+                           "mlp": dict(mlp)} for k in kinds]}
+    llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": ARCH_VOCAB, "hidden_size": width,
+             "intermediate_size": l[3], "num_hidden_layers": len(kinds), "num_attention_heads": l[0],
+             "num_key_value_heads": l[1], "head_dim": l[2], "max_position_embeddings": 8192, "rms_norm_eps": 1e-5,
+             "rope_theta": 500000.0, "tie_word_embeddings": False}
+    return rematar, llama
+
+
+def arch_compare(args, kernels: bool, design: str = "todupel"):
     """Prefill (one prompt of 2,048 tokens) and decode (batches of 8 and 64 holding 2,048 tokens each) of the Todupel design
     and of the Llama shape of equal size, timed with CUDA events; with `kernels`, instead, the device time of every kernel
     of one prefill step and of decode steps at batch 8 that run launch by launch. Prints one JSON line."""
@@ -367,17 +396,25 @@ def arch_compare(args, kernels: bool):
 
     peaks = load_peaks()
     T, HELD_HERE, K = 2048, 2048, max(8, min(args.steps, 64))
-    out = {"metric": "Todupel beside the Llama shape of equal size: prefill and decode tokens/s", "unit": "tokens/s",
+    sizes = ARCH_SIZES if design == "todupel" else REMATAR_SIZES
+    out = {"metric": f"{design.capitalize()} beside the Llama shape of equal size: prefill and decode tokens/s", "unit": "tokens/s",
            "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights, random token ids", "peaks": peaks,
            "config": {"prefill_tokens": T, "decode_context": HELD_HERE, "decode_steps": K, "vocab": ARCH_VOCAB,
                       "l2": "inputs larger than L2: the weights of a model exceed 126 MB"}, "sizes": {}}
     rng = np.random.RandomState(0)
-    for size in ARCH_SIZES:
-        width, layers, heads, kv, dim, inter = ARCH_SIZES[size]
-        rec = {"shape": {"width": width, "layers": layers, "heads": heads, "kv_heads": kv, "map_size": dim,
-                         "value_size": 2 * dim, "llama_head_dim": 2 * dim, "llama_intermediate": inter,
-                         "todupel_ff": inter * 3 // 2}}
-        for which, cfg in zip(("todupel", "llama"), arch_pair(size)):
+    for size in sizes:
+        if design == "todupel":
+            width, layers, heads, kv, dim, inter = ARCH_SIZES[size]
+            rec = {"shape": {"width": width, "layers": layers, "heads": heads, "kv_heads": kv, "map_size": dim,
+                             "value_size": 2 * dim, "llama_head_dim": 2 * dim, "llama_intermediate": inter,
+                             "todupel_ff": inter * 3 // 2}}
+            pair = arch_pair(size)
+        else:
+            width, kinds, s, a, l = REMATAR_SIZES[size]
+            rec = {"shape": {"width": width, "layers": kinds, "ssd": list(s), "latent_attention": list(a), "llama": list(l),
+                             "rematar_ff": l[3] * 3 // 2}}
+            pair = rematar_pair(size)
+        for which, cfg in zip((design, "llama"), pair):
             batches = (8,) if kernels else (8, 64)
             span = 16 + 3 * K + 64
             kv_tokens = max(batches) * (-(-(HELD_HERE + span) // 16) * 16) + 2 * T
@@ -409,7 +446,7 @@ def arch_compare(args, kernels: bool):
                 torch.cuda.synchronize()
                 return a.elapsed_time(b)
 
-            m = {}
+            m = {"weight_bytes": eng.built.model.weight_bytes()}
             for _ in range(3):
                 prefill_once()
             if kernels:
@@ -451,9 +488,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", choices=["decode", "todupel", "todupel-kernels"] + sorted(SERVING), default="decode",
+    ap.add_argument("--workload", choices=["decode", "todupel", "todupel-kernels", "rematar", "rematar-kernels"] + sorted(SERVING), default="decode",
                     help="decode: the default benchmark; serve3b / serve8b: continuous batching of the 3B / 8B workloads; "
-                         "todupel: the Todupel design beside the Llama shape of equal size (todupel-kernels: per kernel)")
+                         "todupel / rematar: that design beside the Llama shape of equal size (todupel-kernels / rematar-kernels: per kernel)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-long", action="store_true", help="skip the points at 8,192 tokens (prefill and decode)")
     ap.add_argument("--no-serve", action="store_true", help="skip the points of the 3B and 8B serving workloads")
@@ -468,8 +505,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
-    if args.workload in ("todupel", "todupel-kernels"):
-        return arch_compare(args, kernels=args.workload == "todupel-kernels")
+    if args.workload in ("todupel", "todupel-kernels", "rematar", "rematar-kernels"):
+        return arch_compare(args, kernels=args.workload.endswith("-kernels"), design=args.workload.split("-")[0])
     if args.workload != "decode":
         return serving(args.workload, args.layers if args.layers != FULL_LAYERS else None)
     W = max(3, args.warmup)

@@ -43,6 +43,8 @@ _SIGNATURES = {
         "dl_rotate_pairs": [_I, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P],
         "dl_head_linear": [_I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _P],
         "dl_latent_attention": [_I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]},
+    "latent_attention_flash": {
+        "dl_latent_attention_flash": [_P, _I, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P]},
     "qk_norm_cache": {
         "dl_qk_norm_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _L, _I, _I, _P, _P, _F, _F, _I, _I, _I, _I, _I, _I,
                                    _I, _I, _P]},
@@ -711,6 +713,39 @@ def latent_attention(qw: torch.Tensor, cache: torch.Tensor, block_table: torch.T
         dtype_code(qw.dtype), _p(qw), qw.stride(0), _p(cache), _p(block_table), block_table.stride(0), _p(positions),
         _p(row_slot), _p(sink), _p(out), out.stride(0), qw.shape[0], heads, kv_rank, rot_dim, page_size, scale, window,
         _stream()), "latent_attention")
+
+
+def latent_flash_fits(kv_rank: int, rot_dim: int) -> bool:
+    """Whether the tensor-core latent attention's shared memory (32 query units and two tiles of 64 records) fits a block."""
+    stride = ((kv_rank + rot_dim + 15) & ~15) + 8
+    return 2 * ((32 + 128) * stride + 32 * 72) + 4 * 256 <= 220 * 1024
+
+
+def latent_attention_flash(qw: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor,
+                           n_tiles: int, sink: Optional[torch.Tensor], out: torch.Tensor, heads: int, kv_rank: int,
+                           rot_dim: int, page_size: int, scale: float, window: int, heads_per_block: int) -> None:
+    """latent_attention on bf16 tensor cores: one block per (query tile, group of `heads_per_block` heads), the tiles
+    int32 [n_tiles, 4] = (request slot, first row, rows, first position) with at most 32 // heads_per_block rows each.
+    See csrc/latent_attention_flash.cu."""
+    _cuda(qw, cache, block_table, tiles, sink, out)
+    _rows_contiguous(qw, "qw")
+    _rows_contiguous(out, "out")
+    rw = kv_rank + rot_dim
+    if any(t.dtype != torch.bfloat16 for t in (qw, cache, out)):
+        raise Unsupported("latent_attention_flash: bfloat16 only")
+    if qw.shape[1] < heads * rw or out.shape[1] < heads * kv_rank or cache.dim() != 3 or cache.shape[1] != page_size \
+            or cache.shape[2] != rw or not cache.is_contiguous():
+        raise InvalidArgument("latent_attention_flash: qw [rows, H*(R+r)], out [rows, H*R], cache contiguous [pages, page_size, R+r]")
+    if tiles.dtype != torch.int32 or tiles.numel() < 4 * n_tiles:
+        raise InvalidArgument("latent_attention_flash: tiles int32 [n_tiles, 4]")
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != heads):
+        raise InvalidArgument("latent_attention_flash: sinks float32 [heads]")
+    check_limits("latent_attention_flash", pages=cache.shape[0], requests=block_table.shape[0], rows=qw.shape[0])
+    _take_ahead()
+    _check(_fn("latent_attention_flash", "dl_latent_attention_flash")(
+        _p(qw), qw.stride(0), _p(cache), _p(block_table), block_table.stride(0), _p(tiles), n_tiles, _p(sink), _p(out),
+        out.stride(0), heads, kv_rank, rot_dim, page_size, scale, window, heads_per_block, _stream()),
+        "latent_attention_flash")
 
 
 def qk_norm_cache_write(qkv: torch.Tensor, positions: torch.Tensor, row_slot: torch.Tensor,

@@ -80,6 +80,11 @@ class LatentAttention:
     def first_weights(self) -> torch.Tensor:
         return self.w_down
 
+    def step_plans(self) -> list:
+        """The query tiles of the step, for the tensor-core kernel (kernels/latent_attention.py)."""
+        from ..kernels import latent_attention as fast
+        return [fast.tile_plan(self.spec)] if fast.flash_applies(self.spec, self.rt.dtype) else []
+
     def cache_spec(self) -> Optional[CacheSpec]:
         s = self.spec
         return CacheSpec(kind="pages", entry_shape=(s.kv_rank + s.rot_dim,), tensors=1, window=int(s.get("window", 0)))
@@ -113,5 +118,8 @@ class LatentAttention:
     def attend(self, wide: torch.Tensor, cache, ctx, out: torch.Tensor) -> None:
         s = self.spec
         (records,) = cache.arrays
+        from ..kernels import latent_attention as fast
+        if fast.attend(wide, cache, ctx, out, s, self.sink):
+            return
         ops.latent_attention(wide, records, cache.block_table, ctx.positions, ctx.row_slot, self.sink, out, s.num_heads,
                              s.kv_rank, s.rot_dim, cache.page_size, float(s.scale), int(s.get("window", 0)))

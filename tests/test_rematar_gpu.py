@@ -378,6 +378,58 @@ def test_attention_over_records_with_a_key_made_to_stand_out(dtype, H, R, r, win
                 f"head {h}, query at {cases[bad][0]} whose key stands {cases[bad][1]} back: {err[bad]:.3g}"
 
 
+@pytest.mark.parametrize("H,R,r,window", [(6, 64, 16, 24), (2, 32, 16, 0), (5, 24, 8, 33), (16, 320, 32, 64), (40, 48, 8, 600),
+                                          (3, 512, 64, 100), (33, 16, 0, 5)])
+def test_tensor_core_attention_over_tiles_of_a_step(H, R, r, window):
+    """The bfloat16 kernel whose blocks take 32 (row, head) units: portions of two requests cut into tiles by the step
+    plan, beside single decoded tokens; every query has a key made to stand out at the window's edge, just outside it,
+    at a key tile's border or at the first token."""
+    from dynalm_b200.kernels import latent_attention as fast
+    from dynalm_b200.kernels import ops
+    from types import SimpleNamespace
+    dtype, page, n_keys, scale = torch.bfloat16, 16, 700, 0.3
+    rng, cache, table, rec = _attention_case(H, R, r, n_keys, page, dtype, seed=H * 10 + R)
+    # the same records serve three requests (their table rows name the same pages): a portion from the first token, a
+    # portion in the middle that crosses key tiles and a chunk border, two single tokens
+    table[0] = table[1]
+    table[2] = table[1]
+    portions = [(1, 0, 75), (0, 600, 1), (2, 430, 97), (1, 699, 1)]              # (slot, first position, rows)
+    w = window if window > 0 else 10 ** 9
+    positions, slots = [], []
+    for slot, first, n in portions:
+        positions += list(range(first, first + n))
+        slots += [slot] * n
+    n = len(positions)
+    q = rng.randn(n, H, R + r) * 0.5
+    for i, pos in enumerate(positions):
+        for h in range(H):
+            dist = [0, w - 1, w, pos % 64, pos % 64 + 1, pos][(i + h) % 6]
+            if 0 <= dist <= pos:
+                target = rec[pos - dist]
+                q[i, h] += (4.0 + h % 5) * target / (scale * np.dot(target, target))
+    q_t = _t(q.reshape(n, -1), dtype)
+    sink = _t(rng.randn(H) + 2.0)
+    spec = SimpleNamespace(num_heads=H, kv_rank=R, rot_dim=r)
+    plan = fast.tile_plan(spec)
+    host = np.zeros(plan.ints(n, len(portions)), dtype=np.int32)
+    q_start = np.cumsum([0] + [p[2] for p in portions])
+    n_tiles = plan.fill(host, SimpleNamespace(q_len=[p[2] for p in portions], q_start=list(q_start[:-1]),
+                                               pos_start=[p[1] for p in portions], slots=[p[0] for p in portions]))
+    assert n_tiles == sum(-(-p[2] // plan.rows) for p in portions) and plan.rows * fast.heads_per_block(H) <= 32
+    tiles = torch.from_numpy(host).to(DEV)
+    out = torch.zeros(n, H * R, dtype=dtype, device=DEV)
+    ops.latent_attention_flash(q_t, cache, table, tiles, n_tiles, sink, out, H, R, r, page, scale, window, fast.heads_per_block(H))
+    got = _np(out).reshape(n, H, R)
+    qf = _np(q_t).reshape(n, H, R + r)
+    for h in range(H):
+        wts = plain.window_sink_softmax((qf[:, h] @ rec.T) * scale, np.asarray(positions), np.arange(n_keys), window,
+                                        float(sink[h]))
+        want = wts @ rec[:, :R]
+        err = np.abs(got[:, h] - want).max(axis=1)
+        bad = int(err.argmax())
+        assert err[bad] <= 3e-2 * max(1.0, np.abs(want).max()), f"head {h}, query at {positions[bad]}: {err[bad]:.3g}"
+
+
 # ---------------------------------------------------------------------------------------------
 # whole models through the step function
 # ---------------------------------------------------------------------------------------------
