@@ -67,49 +67,71 @@ __global__ void ssm_conv_keep_kernel(const T* __restrict__ proj, int proj_stride
 }
 
 // ---- recurrence ---------------------------------------------------------------------------------------------
-// Block = (request, head, slice of PV channels). Thread (p, j) keeps rows n = j, j + NS, j + 2 NS, ... of column p
-// of S in registers (at most NR of them). The request's tokens of this step are walked in tiles of TT: a tile's B, C,
-// x, step sizes and decays go to shared memory, every thread then runs the tile's tokens over its registers and
-// leaves its share of every y in shared memory, and the shares of a channel are added in a fixed order.
-constexpr int SCAN_TT = 8;
+// Block = (run of tokens, head, slice of PV channels). Thread (p, j) keeps rows n = j, j + NS, j + 2 NS, ... of column p
+// of S in registers (at most NR of them). The run's tokens are walked in tiles of TT: a tile's B, C, x, step sizes and
+// decays go to shared memory, every thread then runs the tile's tokens over its registers and leaves its share of every
+// y in shared memory, and the shares of a channel are added in a fixed order.
+//
+// A run is either all the tokens a request brings in this step (SCAN_WHOLE: from the request's state, back into it),
+// or one SEGMENT of a long portion, so that the segments of a portion run side by side in three launches:
+//   SCAN_LOCAL   every segment from a zero state: what it adds to the state, and the product of its decays, to scratch
+//   (carry)      per request, over its segments in order: S_start[c] = the state before segment c (written over the
+//                segment's scratch), S <- decay_c S + added_c; the last S is the request's new state
+//   SCAN_FINISH  every segment again from S_start[c], now with its outputs
+// The recurrence is linear in S, so this is the same arithmetic reordered; all of it is float32.
+constexpr int SCAN_TT = 16;
+constexpr int SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_FINISH = 2;
 
-template <typename T, int NR>
+template <typename T, int NR, int MODE>
 __global__ void ssm_scan_kernel(const T* __restrict__ u, int u_stride,            // [rows, H*P + 2*G*N] after the convolution
                                 const T* __restrict__ proj, int proj_stride, int dt_col,   // dt of head h at proj[row, dt_col + h]
                                 const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                 const float* __restrict__ d_skip, float* __restrict__ state, size_t state_stride,
                                 const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                                const int* __restrict__ segments,                 // [n][4] = (slot, first row, rows, -)
+                                float* __restrict__ scratch, float* __restrict__ seg_decay, int whole_up_to,
                                 float* __restrict__ y, int H, int P, int N, int G, int PV, int NS) {
   extern __shared__ float sm[];
-  float* sB = sm;                               // [TT][N]
-  float* sC = sB + SCAN_TT * N;                 // [TT][N]
-  float* sX = sC + SCAN_TT * N;                 // [TT][PV]
+  float2* sBC = reinterpret_cast<float2*>(sm);  // [TT][N] (B, C)
+  float* sX = sm + 2 * SCAN_TT * N;             // [TT][PV]
   float* sY = sX + SCAN_TT * PV;                // [TT][NS][PV]
   float* sDt = sY + SCAN_TT * NS * PV;          // [TT] step sizes, then [TT] decays
   float* sDa = sDt + SCAN_TT;
-  const int r = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * PV;
+  const int h = blockIdx.y, p0 = blockIdx.z * PV;
   const int tid = threadIdx.x, pl = tid % PV, j = tid / PV;
   const int p = p0 + pl;
   const bool live = p < P;
   const int g = h / (H / G);
   const int inner = H * P;
-  const int r0 = q_start[r], n_tok = q_start[r + 1] - r0;
-  float* S = state + static_cast<size_t>(ck_request(state_slots[r])) * state_stride + static_cast<size_t>(h) * N * P;
+  int r0, n_tok;
+  float* S;
+  if (MODE == SCAN_WHOLE) {
+    const int r = blockIdx.x;
+    r0 = q_start[r];
+    n_tok = q_start[r + 1] - r0;
+    if (n_tok > whole_up_to) return;            // a long portion: its segments are run by the other three launches
+    S = state + static_cast<size_t>(ck_request(state_slots[r])) * state_stride + static_cast<size_t>(h) * N * P;
+  } else {
+    const int4 seg = reinterpret_cast<const int4*>(segments)[blockIdx.x];
+    r0 = seg.y;
+    n_tok = seg.z;
+    S = scratch + (static_cast<size_t>(blockIdx.x) * H + h) * N * P;
+  }
   const float rate = expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
   float s[NR];
 #pragma unroll
   for (int i = 0; i < NR; ++i) {
     const int n = j + i * NS;
-    s[i] = (live && n < N) ? S[static_cast<size_t>(n) * P + p] : 0.0f;
+    s[i] = (MODE != SCAN_LOCAL && live && n < N) ? S[static_cast<size_t>(n) * P + p] : 0.0f;
   }
+  float run_decay = 1.0f;
   for (int t0 = 0; t0 < n_tok; t0 += SCAN_TT) {
     const int tt = min(SCAN_TT, n_tok - t0);
     __syncthreads();                            // the tile before has been read
     for (int i = tid; i < tt * N; i += blockDim.x) {
       const int t = i / N, n = i % N;
       const T* ur = u + static_cast<size_t>(r0 + t0 + t) * u_stride + inner + g * N + n;
-      sB[i] = to_float(ur[0]);
-      sC[i] = to_float(ur[G * N]);
+      sBC[i] = make_float2(to_float(ur[0]), to_float(ur[G * N]));
     }
     for (int i = tid; i < tt * PV; i += blockDim.x) {
       const int t = i / PV, q = p0 + i % PV;
@@ -125,38 +147,75 @@ __global__ void ssm_scan_kernel(const T* __restrict__ u, int u_stride,          
     for (int t = 0; t < tt; ++t) {
       const float dt = sDt[t], da = sDa[t];
       const float xv = sX[t * PV + pl] * dt;
-      const float* b = sB + t * N;
-      const float* c = sC + t * N;
-      float acc0 = 0.0f, acc1 = 0.0f;
+      const float2* bc = sBC + t * N;
+      if (MODE == SCAN_LOCAL) {
+        run_decay *= da;
 #pragma unroll
-      for (int i = 0; i < NR; i += 2) {
-        const int n0 = j + i * NS, n1 = j + (i + 1) * NS;
-        if (n0 < N) {
-          s[i] = fmaf(da, s[i], b[n0] * xv);
-          acc0 = fmaf(s[i], c[n0], acc0);
+        for (int i = 0; i < NR; ++i) {
+          const int n = j + i * NS;
+          if (n < N) s[i] = fmaf(da, s[i], bc[n].x * xv);
         }
-        if (i + 1 < NR && n1 < N) {
-          s[i + 1] = fmaf(da, s[i + 1], b[n1] * xv);
-          acc1 = fmaf(s[i + 1], c[n1], acc1);
+      } else {
+        float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NR; i += 2) {
+          const int n0 = j + i * NS, n1 = j + (i + 1) * NS;
+          if (n0 < N) {
+            const float2 v = bc[n0];
+            s[i] = fmaf(da, s[i], v.x * xv);
+            acc0 = fmaf(s[i], v.y, acc0);
+          }
+          if (i + 1 < NR && n1 < N) {
+            const float2 v = bc[n1];
+            s[i + 1] = fmaf(da, s[i + 1], v.x * xv);
+            acc1 = fmaf(s[i + 1], v.y, acc1);
+          }
         }
+        sY[(t * NS + j) * PV + pl] = acc0 + acc1;
       }
-      sY[(t * NS + j) * PV + pl] = acc0 + acc1;
     }
-    __syncthreads();
-    for (int i = tid; i < tt * PV; i += blockDim.x) {
-      const int t = i / PV, q = i % PV;
-      if (p0 + q < P) {
-        float sum = 0.0f;
-        for (int k = 0; k < NS; ++k) sum += sY[(t * NS + k) * PV + q];
-        y[static_cast<size_t>(r0 + t0 + t) * inner + h * P + p0 + q] = fmaf(skip, sX[t * PV + q], sum);
+    if (MODE != SCAN_LOCAL) {
+      __syncthreads();
+      for (int i = tid; i < tt * PV; i += blockDim.x) {
+        const int t = i / PV, q = i % PV;
+        if (p0 + q < P) {
+          float sum = 0.0f;
+          for (int k = 0; k < NS; ++k) sum += sY[(t * NS + k) * PV + q];
+          y[static_cast<size_t>(r0 + t0 + t) * inner + h * P + p0 + q] = fmaf(skip, sX[t * PV + q], sum);
+        }
       }
     }
   }
+  if (MODE != SCAN_FINISH) {
 #pragma unroll
-  for (int i = 0; i < NR; ++i) {
-    const int n = j + i * NS;
-    if (live && n < N) S[static_cast<size_t>(n) * P + p] = s[i];
+    for (int i = 0; i < NR; ++i) {
+      const int n = j + i * NS;
+      if (live && n < N) S[static_cast<size_t>(n) * P + p] = s[i];
+    }
   }
+  if (MODE == SCAN_LOCAL && tid == 0 && blockIdx.z == 0) seg_decay[static_cast<size_t>(blockIdx.x) * H + h] = run_decay;
+}
+
+// Between the two passes over the segments of long portions: per request of `long_requests` (first segment, segments,
+// slot, -) and element of the state, the state before every segment in place of what the segment added, and the
+// request's new state.
+__global__ void ssm_carry_kernel(float* __restrict__ state, size_t state_stride, float* __restrict__ scratch,
+                                 const float* __restrict__ seg_decay, const int* __restrict__ long_requests, int H,
+                                 int per_head) {
+  const int4 req = reinterpret_cast<const int4*>(long_requests)[blockIdx.y];
+  const size_t per_seg = static_cast<size_t>(H) * per_head;
+  const size_t e = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= per_seg) return;
+  const int h = static_cast<int>(e / per_head);
+  float* slot = state + static_cast<size_t>(ck_request(req.z)) * state_stride;
+  float S = slot[e];
+  for (int c = 0; c < req.y; ++c) {
+    const size_t seg = static_cast<size_t>(req.x + c);
+    const float added = scratch[seg * per_seg + e];
+    scratch[seg * per_seg + e] = S;
+    S = fmaf(seg_decay[seg * H + h], S, added);
+  }
+  slot[e] = S;
 }
 
 // ---- gated norm -----------------------------------------------------------------------------------------------
@@ -226,12 +285,19 @@ DL_EXPORT int dl_ssm_conv_keep(int dtype, const void* proj, int proj_stride, int
 }
 
 // u: the convolution's output [rows, H*P + 2*G*N]; proj: the projection (for dt); y: float32 [rows, H*P].
+// Requests that bring at most `whole_up_to` tokens run from and into their state in one launch. The longer ones come cut
+// into `n_segments` segments (segments: [n][4] = (slot, first row, rows, -), request by request and in order;
+// long_requests: [n_long][4] = (first segment, segments, slot, -)) and run in three more launches through
+// scratch (float32 [n_segments, H, N, P]) and seg_decay (float32 [n_segments, H]).
 DL_EXPORT int dl_ssm_scan(int dtype, const void* u, int u_stride, const void* proj, int proj_stride, int dt_col,
                           const float* dt_bias, const float* a_log, const float* d_skip, float* state,
                           long long state_stride, const int* q_start, const int* state_slots, float* y, int requests, int H,
-                          int P, int N, int G, cudaStream_t stream) {
+                          int P, int N, int G, int whole_up_to, const int* segments, int n_segments,
+                          const int* long_requests, int n_long, float* scratch, float* seg_decay, cudaStream_t stream) {
   if (requests <= 0) return 0;
-  if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G != 0 || H > 65535) return DL_ERR_UNSUPPORTED;
+  if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G != 0 || H > 65535 || n_long > 65535) return DL_ERR_UNSUPPORTED;
+  if (n_segments > 0 && (segments == nullptr || long_requests == nullptr || scratch == nullptr || seg_decay == nullptr))
+    return DL_ERR_UNSUPPORTED;
   // rows of S per thread: 32 at most; NS threads share a channel
   const int NR = N <= 8 ? 8 : (N <= 64 ? 16 : 32);
   const int NS = (N + NR - 1) / NR;
@@ -243,25 +309,37 @@ DL_EXPORT int dl_ssm_scan(int dtype, const void* u, int u_stride, const void* pr
   const int threads = PV * NS;
   const size_t smem = sizeof(float) * (static_cast<size_t>(dl::SCAN_TT) * (2 * N + PV + NS * PV) + 2 * dl::SCAN_TT);
   if (smem > 200 * 1024) return DL_ERR_UNSUPPORTED;
-  dim3 grid(requests, H, slices);
-#define DL_LAUNCH(T, R)                                                                                               \
+#define DL_LAUNCH(T, R, MODE, BLOCKS)                                                                                 \
   do {                                                                                                                \
     if (smem > 48 * 1024)                                                                                             \
-      cudaFuncSetAttribute(dl::ssm_scan_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
-    dl::ssm_scan_kernel<T, R><<<grid, threads, smem, stream>>>(static_cast<const T*>(u), u_stride, static_cast<const T*>(proj), \
-                                                               proj_stride, dt_col, dt_bias, a_log, d_skip, state,    \
-                                                               static_cast<size_t>(state_stride), q_start, state_slots, \
-                                                               y, H, P, N, G, PV, NS);                                \
+      cudaFuncSetAttribute(dl::ssm_scan_kernel<T, R, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    dl::ssm_scan_kernel<T, R, MODE><<<dim3(BLOCKS, H, slices), threads, smem, stream>>>(                               \
+        static_cast<const T*>(u), u_stride, static_cast<const T*>(proj), proj_stride, dt_col, dt_bias, a_log, d_skip,  \
+        state, static_cast<size_t>(state_stride), q_start, state_slots, segments, scratch, seg_decay, whole_up_to, y,  \
+        H, P, N, G, PV, NS);                                                                                           \
   } while (0)
-#define DL_PICK(T)                   \
-  do {                               \
-    if (NR == 8) DL_LAUNCH(T, 8);    \
-    else if (NR == 16) DL_LAUNCH(T, 16); \
-    else DL_LAUNCH(T, 32);           \
+#define DL_PICK(T, MODE, BLOCKS)                      \
+  do {                                                \
+    if (NR == 8) DL_LAUNCH(T, 8, MODE, BLOCKS);       \
+    else if (NR == 16) DL_LAUNCH(T, 16, MODE, BLOCKS); \
+    else DL_LAUNCH(T, 32, MODE, BLOCKS);              \
   } while (0)
-  if (dtype == 0) DL_PICK(float);
-  else if (dtype == 1) DL_PICK(dl::bf16);
-  else return DL_ERR_UNSUPPORTED;
+#define DL_MODE(MODE, BLOCKS)                         \
+  do {                                                \
+    if (dtype == 0) DL_PICK(float, MODE, BLOCKS);     \
+    else DL_PICK(dl::bf16, MODE, BLOCKS);             \
+  } while (0)
+  if (dtype != 0 && dtype != 1) return DL_ERR_UNSUPPORTED;
+  DL_MODE(dl::SCAN_WHOLE, requests);
+  if (n_segments > 0) {
+    DL_MODE(dl::SCAN_LOCAL, n_segments);
+    const int per_head = N * P;
+    const size_t per_seg = static_cast<size_t>(H) * per_head;
+    dl::ssm_carry_kernel<<<dim3(static_cast<unsigned>((per_seg + 255) / 256), n_long), 256, 0, stream>>>(
+        state, static_cast<size_t>(state_stride), scratch, seg_decay, long_requests, H, per_head);
+    DL_MODE(dl::SCAN_FINISH, n_segments);
+  }
+#undef DL_MODE
 #undef DL_PICK
 #undef DL_LAUNCH
   return dl::launch_status();

@@ -36,7 +36,8 @@ _SIGNATURES = {
     "ssm": {
         "dl_ssm_conv": [_I, _P, _I, _I, _I, _P, _P, _I, _P, _L, _L, _P, _P, _P, _P, _P, _I, _P],
         "dl_ssm_conv_keep": [_I, _P, _I, _I, _I, _I, _P, _L, _L, _P, _P, _I, _P],
-        "dl_ssm_scan": [_I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "dl_ssm_scan": [_I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _P,
+                        _P, _P],
         "dl_gated_group_norm": [_I, _P, _P, _I, _P, _F, _P, _I, _I, _I, _P]},
     "latent_attention": {
         "dl_latent_prep": [_I, _P, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _I, _P, _P, _I, _P],
@@ -584,13 +585,66 @@ def ssm_conv_keep(proj: torch.Tensor, col0: int, channels: int, K: int, state: t
            "ssm_conv_keep")
 
 
+SSM_SEGMENT = 128      # tokens to a segment of a long portion, and the most a request brings to run as one piece
+
+
+class SsmSegmentPlan:
+    """The step plan of the state-space recurrence: the requests that bring more than SSM_SEGMENT tokens, cut into
+    segments of at most that many, so that the segments of a portion run side by side (csrc/ssm.cu). int32 rows of 4:
+    first a table of the long requests (first segment, segments, slot, 0), a third of the section's rows; behind it
+    the segments (slot, first row of the step, rows, 0), request by request and in order. A step of T tokens has at
+    most T // (SSM_SEGMENT + 1) long requests and T // SSM_SEGMENT segments more than that. `fill` returns (segments,
+    long requests, rows of the table)."""
+
+    name = "ssm_segments"
+
+    def ints(self, max_tokens: int, max_requests: int) -> int:
+        table = max(1, max_tokens // (SSM_SEGMENT + 1))
+        return 4 * (2 * table + max_tokens // SSM_SEGMENT)
+
+    @staticmethod
+    def table_rows(section_ints: int) -> int:
+        """Rows of the long requests' table in a section of that many integers: max_tokens // SSM_SEGMENT is the
+        table's rows or one more, so the table is a third of the section, rounded down."""
+        return max(1, section_ints // 12)
+
+    def fill(self, host, shape):
+        table = self.table_rows(len(host))
+        longs, segs = [], []
+        for n, r0, slot in zip(shape.q_len, shape.q_start, shape.slots):
+            if n <= SSM_SEGMENT:
+                continue
+            first = len(segs)
+            for t0 in range(0, n, SSM_SEGMENT):
+                segs.append((slot, r0 + t0, min(SSM_SEGMENT, n - t0), 0))
+            longs.append((first, len(segs) - first, slot, 0))
+        if len(longs) > table or 4 * (table + len(segs)) > len(host):
+            raise InvalidArgument("more long portions in a step than the step's buffers were made for")
+        flat = [v for t in longs for v in t]
+        host[:len(flat)] = flat
+        flat = [v for t in segs for v in t]
+        host[4 * table:4 * table + len(flat)] = flat
+        return len(segs), len(longs), table
+
+    @staticmethod
+    def most_segments(max_tokens: int) -> int:
+        return max_tokens // SSM_SEGMENT + max(1, max_tokens // (SSM_SEGMENT + 1))
+
+
+SSM_SEGMENTS = SsmSegmentPlan()
+
+
 def ssm_scan(u: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
              d_skip: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, state_slots: torch.Tensor, y: torch.Tensor,
-             requests: int, heads: int, head_dim: int, n_state: int, groups: int) -> None:
+             requests: int, heads: int, head_dim: int, n_state: int, groups: int, planned=None,
+             scratch: Optional[torch.Tensor] = None, seg_decay: Optional[torch.Tensor] = None) -> None:
     """The recurrence of every head over every request's rows of the step, from and into state[slot, :H*N*P] ([H, N,
     P]). u: [rows, H*P + 2*G*N] after the convolution (x | B | C); proj[row, dt_col + h]: the raw step size; y:
-    float32 [rows, H*P]. See csrc/ssm.cu."""
-    _cuda(u, proj, dt_bias, a_log, d_skip, state, q_start, state_slots, y)
+    float32 [rows, H*P]. `planned` = (the SsmSegmentPlan's integers on the device, what its fill returned): requests
+    that bring more than SSM_SEGMENT tokens run as segments side by side, through `scratch` (float32, [segments, H*N*P]
+    at least) and `seg_decay` (float32, [segments, H]); without it every request must bring at most SSM_SEGMENT tokens
+    or runs as one piece however long it is. See csrc/ssm.cu."""
+    _cuda(u, proj, dt_bias, a_log, d_skip, state, q_start, state_slots, y, scratch, seg_decay)
     _rows_contiguous(u, "u")
     _rows_contiguous(proj, "proj")
     inner = heads * head_dim
@@ -602,10 +656,20 @@ def ssm_scan(u: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Te
         raise InvalidArgument("ssm_scan: state float32 [slots, >= H*N*P]")
     if y.dtype != torch.float32 or not y.is_contiguous() or y.shape != (u.shape[0], inner):
         raise InvalidArgument("ssm_scan: y float32 contiguous [rows, H*P]")
+    whole_up_to, segs, n_segs, longs, n_long = 1 << 30, None, 0, None, 0
+    if planned is not None:
+        ints, (n_segs, n_long, long_cap) = planned
+        if n_segs:
+            if scratch is None or seg_decay is None or scratch.dtype != torch.float32 or seg_decay.dtype != torch.float32 \
+                    or scratch.numel() < n_segs * inner * n_state or seg_decay.numel() < n_segs * heads:
+                raise InvalidArgument("ssm_scan: scratch float32 [segments, H*N*P] and seg_decay float32 [segments, H]")
+            longs, segs = ints, ints[4 * long_cap:]
+        whole_up_to = SSM_SEGMENT
     check_limits("ssm", requests=state.shape[0], rows=u.shape[0])
     _check(_fn("ssm", "dl_ssm_scan")(dtype_code(u.dtype), _p(u), u.stride(0), _p(proj), proj.stride(0), dt_col, _p(dt_bias),
                                       _p(a_log), _p(d_skip), _p(state), state.stride(0), _p(q_start), _p(state_slots),
-                                      _p(y), requests, heads, head_dim, n_state, groups, _stream()), "ssm_scan")
+                                      _p(y), requests, heads, head_dim, n_state, groups, whole_up_to, _p(segs), n_segs,
+                                      _p(longs), n_long, _p(scratch), _p(seg_decay), _stream()), "ssm_scan")
 
 
 def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, parts: int,

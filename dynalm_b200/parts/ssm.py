@@ -71,6 +71,10 @@ class StateSpaceMixer:
     def first_weights(self) -> torch.Tensor:
         return self.w_in
 
+    def step_plans(self) -> list:
+        """The segments that long portions are cut into, for the recurrence (kernels/ops.SsmSegmentPlan)."""
+        return [ops.SSM_SEGMENTS]
+
     def cache_spec(self) -> Optional[CacheSpec]:
         s = self.spec
         return CacheSpec(kind="state", state_shape=(self.keep_off + (s.taps - 1) * self.channels,), dtype="float32")
@@ -91,8 +95,15 @@ class StateSpaceMixer:
         ops.ssm_conv_keep(proj, self.inner, self.channels, s.taps, state, self.keep_off, ctx.q_start, ctx.state_slots,
                           ctx.num_requests)
         y = rt.buffer("ssd_y", (rows, self.inner), torch.float32)
+        planned = ctx.extras.get(ops.SSM_SEGMENTS.name)
+        scratch = seg_decay = None
+        if planned is not None and planned[1][0]:
+            # (sized once for the most segments a step of the runtime's size can have; shared by all layers of these sizes)
+            most = ops.SSM_SEGMENTS.most_segments(rt.max_tokens)
+            scratch = rt.flat(f"ssd_segment_states_{self.keep_off}", most * self.keep_off)
+            seg_decay = rt.flat(f"ssd_segment_decays_{H}", most * H)
         ops.ssm_scan(u, proj, self.inner + self.channels, self.dt_bias, self.a_log, self.d, state, ctx.q_start,
-                     ctx.state_slots, y, ctx.num_requests, H, P, N, G)
+                     ctx.state_slots, y, ctx.num_requests, H, P, N, G, planned, scratch, seg_decay)
         g = rt.buffer("ssd_gated", (rows, self.inner))
         ops.gated_group_norm(y, proj, self.norm, self.eps, s.norm_groups, g)
         return linear_partial(g, self.w_o, rt, "mixer_out")

@@ -231,6 +231,64 @@ def test_recurrence_in_portions_keeps_its_state(dtype, H, P, N, G):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,P,N,G", [(4, 32, 64, 2), (5, 20, 12, 1), (2, 64, 128, 1)])
+def test_long_portions_run_as_segments_side_by_side(dtype, H, P, N, G):
+    """Portions longer than a segment are cut by the step plan and run in three launches; shorter ones beside them run
+    as one piece; a second step goes on from the states the first left (one of its requests long again)."""
+    from types import SimpleNamespace
+    from dynalm_b200.kernels import ops
+    rng = np.random.RandomState(H + P + N)
+    seg = ops.SSM_SEGMENT
+    inner, dt_col, width = H * P, 1, 1 + H
+    a_log = rng.randn(H) * 0.3
+    a_log[0] = -7.0                                                            # a head that forgets almost nothing
+    dt_bias, d_skip = rng.randn(H) * 0.3, 1 + 0.2 * rng.randn(H)
+    steps = [{0: 2 * seg + 37, 2: 5, 3: seg, 1: seg + 1}, {0: seg + 3, 2: 1, 3: 2}]     # slot -> tokens brought
+    total = {s: sum(st.get(s, 0) for st in steps) for s in range(4)}
+    seqs, want = {}, {}
+    for s, n in total.items():
+        u = rng.randn(n, inner + 2 * G * N) * 0.7
+        u[0, :inner] *= 6.0
+        dt_raw = rng.randn(n, H)
+        u_t, dt_t = _np(_t(u, dtype)), _np(_t(dt_raw, dtype))
+        seqs[s] = (u, dt_raw)
+        per = H // G
+        B = np.repeat(u_t[:, inner:inner + G * N].reshape(n, G, N), per, axis=1)
+        C = np.repeat(u_t[:, inner + G * N:].reshape(n, G, N), per, axis=1)
+        want[s], _ = plain.ssm_scan(u_t[:, :inner].reshape(n, H, P), plain.softplus(dt_t + dt_bias), B, C, a_log, d_skip)
+    state = torch.zeros(4, inner * N + 3, device=DEV)
+    plan = ops.SSM_SEGMENTS
+    max_tokens = 512
+    at = {s: 0 for s in total}
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    for st in steps:
+        batch = [(s, at[s], n) for s, n in st.items()]
+        rows = sum(n for _, _, n in batch)
+        u = torch.cat([_t(seqs[s][0][f:f + n], dtype) for s, f, n in batch])
+        proj = torch.zeros(rows, width, dtype=dtype, device=DEV)
+        proj[:, dt_col:dt_col + H] = torch.cat([_t(seqs[s][1][f:f + n], dtype) for s, f, n in batch])
+        _, _, _, q_start, _, slots = _step_arrays([(f, n) for _, f, n in batch], [s for s, _, _ in batch])
+        host = np.zeros(plan.ints(max_tokens, 4), dtype=np.int32)
+        meta = plan.fill(host, SimpleNamespace(q_len=[n for _, _, n in batch], q_start=[int(v) for v in q_start.cpu()[:-1]],
+                                               slots=[s for s, _, _ in batch]))
+        assert meta[0] == sum(-(-n // seg) for _, _, n in batch if n > seg) and meta[1] == sum(n > seg for _, _, n in batch)
+        most = plan.most_segments(max_tokens)
+        scratch = torch.full((most * inner * N,), float("nan"), device=DEV)     # whatever it held before must not matter
+        decay = torch.full((most * H,), float("nan"), device=DEV)
+        y = torch.zeros(rows, inner, device=DEV)
+        ops.ssm_scan(u, proj, dt_col, _t(dt_bias), _t(a_log), _t(d_skip), state, q_start, slots, y, len(batch), H, P, N, G,
+                     (torch.from_numpy(host).to(DEV), meta), scratch, decay)
+        r0 = 0
+        for s, first, n in batch:
+            ref = want[s][first:first + n].reshape(n, inner)
+            err = np.abs(_np(y[r0:r0 + n]) - ref).max(axis=1)
+            bad = int(err.argmax())
+            assert err[bad] <= tol * max(1.0, np.abs(ref).max()), f"slot {s}, token {first + bad}: {err[bad]:.3g}"
+            r0 += n
+            at[s] += n
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gate_comes_before_the_norm_of_every_part(dtype):
     from dynalm_b200.kernels import ops
     rng = np.random.RandomState(8)
