@@ -67,8 +67,8 @@ __global__ void ssm_conv_keep_kernel(const T* __restrict__ proj, int proj_stride
 }
 
 // ---- recurrence ---------------------------------------------------------------------------------------------
-// Block = (run of tokens, head, slice of PV channels). Thread (p, j) keeps rows n = j, j + NS, j + 2 NS, ... of column p
-// of S in registers (at most NR of them). The run's tokens are walked in tiles of TT: a tile's B, C, x, step sizes and
+// Block = (run of tokens, head, slice of PV channels). Thread (p, j) keeps rows n = j NR .. j NR + NR - 1 of column p
+// of S in registers (FULL: N = NS NR, no row of a thread lies outside). The run's tokens are walked in tiles of TT: a tile's B, C, x, step sizes and
 // decays go to shared memory, every thread then runs the tile's tokens over its registers and leaves its share of every
 // y in shared memory, and the shares of a channel are added in a fixed order.
 //
@@ -82,8 +82,8 @@ __global__ void ssm_conv_keep_kernel(const T* __restrict__ proj, int proj_stride
 constexpr int SCAN_TT = 16;
 constexpr int SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_FINISH = 2;
 
-template <typename T, int NR, int MODE>
-__global__ void ssm_scan_kernel(const T* __restrict__ u, int u_stride,            // [rows, H*P + 2*G*N] after the convolution
+template <typename T, int NR, int MODE, bool FULL>
+__global__ void __launch_bounds__(256, 3) ssm_scan_kernel(const T* __restrict__ u, int u_stride,            // [rows, H*P + 2*G*N] after the convolution
                                 const T* __restrict__ proj, int proj_stride, int dt_col,   // dt of head h at proj[row, dt_col + h]
                                 const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                 const float* __restrict__ d_skip, float* __restrict__ state, size_t state_stride,
@@ -118,12 +118,11 @@ __global__ void ssm_scan_kernel(const T* __restrict__ u, int u_stride,          
     S = scratch + (static_cast<size_t>(blockIdx.x) * H + h) * N * P;
   }
   const float rate = expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
+  const int n_first = j * NR;                    // this thread's rows of S: n_first + i
   float s[NR];
 #pragma unroll
-  for (int i = 0; i < NR; ++i) {
-    const int n = j + i * NS;
-    s[i] = (MODE != SCAN_LOCAL && live && n < N) ? S[static_cast<size_t>(n) * P + p] : 0.0f;
-  }
+  for (int i = 0; i < NR; ++i)
+    s[i] = (MODE != SCAN_LOCAL && live && (FULL || n_first + i < N)) ? S[static_cast<size_t>(n_first + i) * P + p] : 0.0f;
   float run_decay = 1.0f;
   for (int t0 = 0; t0 < n_tok; t0 += SCAN_TT) {
     const int tt = min(SCAN_TT, n_tok - t0);
@@ -147,32 +146,28 @@ __global__ void ssm_scan_kernel(const T* __restrict__ u, int u_stride,          
     for (int t = 0; t < tt; ++t) {
       const float dt = sDt[t], da = sDa[t];
       const float xv = sX[t * PV + pl] * dt;
-      const float2* bc = sBC + t * N;
-      if (MODE == SCAN_LOCAL) {
-        run_decay *= da;
+      const float2* bc = sBC + t * N + n_first;
+      if (MODE == SCAN_LOCAL) run_decay *= da;
+      float acc0 = 0.0f, acc1 = 0.0f;
 #pragma unroll
-        for (int i = 0; i < NR; ++i) {
-          const int n = j + i * NS;
-          if (n < N) s[i] = fmaf(da, s[i], bc[n].x * xv);
+      for (int i = 0; i < NR; i += 2) {
+        float2 v0, v1;
+        if (FULL) {                              // two rows' (B, C) in one 16-byte load: N and NR are even
+          const float4 q = *reinterpret_cast<const float4*>(bc + i);
+          v0 = make_float2(q.x, q.y);
+          v1 = make_float2(q.z, q.w);
+        } else {
+          v0 = n_first + i < N ? bc[i] : make_float2(0.f, 0.f);
+          v1 = n_first + i + 1 < N ? bc[i + 1] : make_float2(0.f, 0.f);
         }
-      } else {
-        float acc0 = 0.0f, acc1 = 0.0f;
-#pragma unroll
-        for (int i = 0; i < NR; i += 2) {
-          const int n0 = j + i * NS, n1 = j + (i + 1) * NS;
-          if (n0 < N) {
-            const float2 v = bc[n0];
-            s[i] = fmaf(da, s[i], v.x * xv);
-            acc0 = fmaf(s[i], v.y, acc0);
-          }
-          if (i + 1 < NR && n1 < N) {
-            const float2 v = bc[n1];
-            s[i + 1] = fmaf(da, s[i + 1], v.x * xv);
-            acc1 = fmaf(s[i + 1], v.y, acc1);
-          }
+        s[i] = fmaf(da, s[i], v0.x * xv);
+        s[i + 1] = fmaf(da, s[i + 1], v1.x * xv);
+        if (MODE != SCAN_LOCAL) {
+          acc0 = fmaf(s[i], v0.y, acc0);
+          acc1 = fmaf(s[i + 1], v1.y, acc1);
         }
-        sY[(t * NS + j) * PV + pl] = acc0 + acc1;
       }
+      if (MODE != SCAN_LOCAL) sY[(t * NS + j) * PV + pl] = acc0 + acc1;
     }
     if (MODE != SCAN_LOCAL) {
       __syncthreads();
@@ -188,10 +183,8 @@ __global__ void ssm_scan_kernel(const T* __restrict__ u, int u_stride,          
   }
   if (MODE != SCAN_FINISH) {
 #pragma unroll
-    for (int i = 0; i < NR; ++i) {
-      const int n = j + i * NS;
-      if (live && n < N) S[static_cast<size_t>(n) * P + p] = s[i];
-    }
+    for (int i = 0; i < NR; ++i)
+      if (live && (FULL || n_first + i < N)) S[static_cast<size_t>(n_first + i) * P + p] = s[i];
   }
   if (MODE == SCAN_LOCAL && tid == 0 && blockIdx.z == 0) seg_decay[static_cast<size_t>(blockIdx.x) * H + h] = run_decay;
 }
@@ -302,27 +295,29 @@ DL_EXPORT int dl_ssm_scan(int dtype, const void* u, int u_stride, const void* pr
   const int NR = N <= 8 ? 8 : (N <= 64 ? 16 : 32);
   const int NS = (N + NR - 1) / NR;
   if (NS > 32) return DL_ERR_UNSUPPORTED;                          // N up to 1,024
-  int PV = P < 32 ? P : 32;
-  while (PV * 2 <= P && PV * 2 * NS <= 256) PV *= 2;
+  const bool full = NS * NR == N && N % 2 == 0;
+  int PV = 256 / NS;                                               // channels to a block: at most 256 threads
+  if (PV > P) PV = P;
+  if (PV > 32) PV &= ~31;                                          // whole warps share a j
   const int slices = (P + PV - 1) / PV;
   if (slices > 65535) return DL_ERR_UNSUPPORTED;
   const int threads = PV * NS;
   const size_t smem = sizeof(float) * (static_cast<size_t>(dl::SCAN_TT) * (2 * N + PV + NS * PV) + 2 * dl::SCAN_TT);
   if (smem > 200 * 1024) return DL_ERR_UNSUPPORTED;
-#define DL_LAUNCH(T, R, MODE, BLOCKS)                                                                                 \
+#define DL_LAUNCH(T, R, MODE, F, BLOCKS)                                                                              \
   do {                                                                                                                \
     if (smem > 48 * 1024)                                                                                             \
-      cudaFuncSetAttribute(dl::ssm_scan_kernel<T, R, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
-    dl::ssm_scan_kernel<T, R, MODE><<<dim3(BLOCKS, H, slices), threads, smem, stream>>>(                               \
+      cudaFuncSetAttribute(dl::ssm_scan_kernel<T, R, MODE, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    dl::ssm_scan_kernel<T, R, MODE, F><<<dim3(BLOCKS, H, slices), threads, smem, stream>>>(                            \
         static_cast<const T*>(u), u_stride, static_cast<const T*>(proj), proj_stride, dt_col, dt_bias, a_log, d_skip,  \
         state, static_cast<size_t>(state_stride), q_start, state_slots, segments, scratch, seg_decay, whole_up_to, y,  \
         H, P, N, G, PV, NS);                                                                                           \
   } while (0)
-#define DL_PICK(T, MODE, BLOCKS)                      \
-  do {                                                \
-    if (NR == 8) DL_LAUNCH(T, 8, MODE, BLOCKS);       \
-    else if (NR == 16) DL_LAUNCH(T, 16, MODE, BLOCKS); \
-    else DL_LAUNCH(T, 32, MODE, BLOCKS);              \
+#define DL_PICK(T, MODE, BLOCKS)                                                          \
+  do {                                                                                    \
+    if (NR == 8) { if (full) DL_LAUNCH(T, 8, MODE, true, BLOCKS); else DL_LAUNCH(T, 8, MODE, false, BLOCKS); }        \
+    else if (NR == 16) { if (full) DL_LAUNCH(T, 16, MODE, true, BLOCKS); else DL_LAUNCH(T, 16, MODE, false, BLOCKS); } \
+    else { if (full) DL_LAUNCH(T, 32, MODE, true, BLOCKS); else DL_LAUNCH(T, 32, MODE, false, BLOCKS); }              \
   } while (0)
 #define DL_MODE(MODE, BLOCKS)                         \
   do {                                                \

@@ -44,6 +44,8 @@ _SIGNATURES = {
         "dl_rotate_pairs": [_I, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P],
         "dl_head_linear": [_I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _P],
         "dl_latent_attention": [_I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]},
+    "head_linear_tc": {
+        "dl_head_linear_tc": [_P, _I, _I, _I, _P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _P]},
     "latent_attention_flash": {
         "dl_latent_attention_flash": [_P, _I, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P]},
     "qk_norm_cache": {
@@ -751,9 +753,18 @@ def head_linear(x: torch.Tensor, head_in: int, n_in: int, w: torch.Tensor, out: 
         _rows_contiguous(gate, "gate")
         if gate.dtype != x.dtype or gate.shape[0] < x.shape[0] or (H - 1) * gate_head + n_out > gate.shape[1]:
             raise InvalidArgument("head_linear: the gate's pieces do not fit")
+    gate_stride = gate.stride(0) if gate is not None else 0
+    if (x.dtype == torch.bfloat16 and n_in % 8 == 0 and n_out % 8 == 0 and x.stride(0) % 8 == 0 and head_in % 8 == 0
+            and out.stride(0) % 2 == 0 and head_out % 2 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and out.data_ptr() % 4 == 0):
+        # the tensor-core kernel (csrc/head_linear_tc.cu)
+        _check(_fn("head_linear_tc", "dl_head_linear_tc")(
+            _p(x), x.stride(0), head_in, n_in, _p(w), n_out, _p(out), out.stride(0), head_out, _p(gate), gate_stride,
+            gate_head, x.shape[0], H, _stream()), "head_linear")
+        return
     _check(_fn("latent_attention", "dl_head_linear")(
         dtype_code(x.dtype), _p(x), x.stride(0), head_in, n_in, _p(w), n_out, _p(out), out.stride(0), head_out, _p(gate),
-        gate.stride(0) if gate is not None else 0, gate_head, x.shape[0], H, _stream()), "head_linear")
+        gate_stride, gate_head, x.shape[0], H, _stream()), "head_linear")
 
 
 def latent_attention(qw: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor,

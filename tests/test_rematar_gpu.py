@@ -359,7 +359,9 @@ def test_latents_are_normed_keys_turned_and_records_land_in_their_pages(dtype, q
 def test_per_head_products(dtype, rows):
     from dynalm_b200.kernels import ops
     rng = np.random.RandomState(rows)
-    for H, n_in, n_out, head_in, head_out in ((4, 16, 48, 24, 56), (3, 44, 28, 44, 28), (2, 320, 64, 320, 64), (5, 7, 150, 9, 150)):
+    # (sizes in multiples of 8 take the tensor-core kernel in bfloat16, the others the plain one)
+    for H, n_in, n_out, head_in, head_out in ((4, 16, 48, 24, 56), (3, 44, 28, 44, 28), (2, 320, 64, 320, 64), (5, 7, 150, 9, 150),
+                                              (3, 40, 72, 48, 80), (2, 136, 200, 136, 200)):
         x = _t(rng.randn(rows, (H - 1) * head_in + n_in + 3), dtype)
         w = _t(rng.randn(H, n_in, n_out) * 0.3, dtype)
         gate = _t(rng.randn(rows, H * n_out + 4) * 2, dtype)
