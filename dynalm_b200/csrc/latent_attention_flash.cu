@@ -70,6 +70,8 @@ struct LatentFlashParams {
   int out_stride;
   int H, R, r, page_size, window, HG;      // HG heads of QR = 32 / HG rows to a block (one row when HG = 32)
   float scale;
+  int parts;               // > 1: the key tiles of every query tile are dealt over this many blocks (blockIdx.z), which
+  float* scratch;          // leave (max, sum, O) per unit in scratch [row, head, part, R + 2] for the merge kernel
 };
 
 // Records of keys [t0, t0 + 64) into a stage: a warp takes 8 keys, its lanes a key's 16-byte pieces. Keys outside
@@ -133,7 +135,12 @@ latent_attention_flash_kernel(const LatentFlashParams p) {
   }
   for (int i = tid; i < 4 * LF_M; i += LF_THREADS) sPSum[i] = 0.0f;
 
-  const int first_tile = lo / LF_KT, last_tile = hi / LF_KT;
+  int first_tile = lo / LF_KT, last_tile = hi / LF_KT;
+  if (p.parts > 1) {                                         // this block's share of the key tiles (it may be empty)
+    const int per = (last_tile - first_tile + p.parts) / p.parts;
+    first_tile += static_cast<int>(blockIdx.z) * per;
+    last_tile = min(last_tile, first_tile + per - 1);
+  }
   lf_load_keys(p, table, sK, RS, RW, first_tile * LF_KT, lo, hi, warp, lane);
   lf_commit();
 
@@ -269,6 +276,30 @@ latent_attention_flash_kernel(const LatentFlashParams p) {
       }
     }
   }
+  if (p.parts > 1) {
+    // ---- a part: (max, sum, O) of every unit to scratch; the merge kernel finishes --------------------------------------
+    lf_wait<0>();                                            // (a part without key tiles has its one load in flight)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (!uok[i]) continue;
+      const int u = (i >> 1) * 16 + (i & 1) * 8 + g;
+      const int ur = u / p.HG, uh = u % p.HG;
+      float* rec = p.scratch + ((static_cast<size_t>(row0 + ur) * p.H + h0 + uh) * p.parts + blockIdx.z) * (p.R + 2);
+      if (warp == 0 && q4 == 0) {
+        rec[0] = m_run[i];
+        rec[1] = l_run[i];
+      }
+#pragma unroll
+      for (int b = 0; b < NT; ++b) {
+        const int col = (warp * NT + b) * 8 + q4 * 2;
+        if (col < p.R) {
+          const int a = i >> 1, j = (i & 1) * 2;
+          *reinterpret_cast<float2*>(rec + 2 + col) = make_float2(o[a][b][j], o[a][b][j + 1]);
+        }
+      }
+    }
+    return;
+  }
   // ---- the sink joins the denominator; O / denominator out ---------------------------------------------------------
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -295,6 +326,32 @@ latent_attention_flash_kernel(const LatentFlashParams p) {
   }
 }
 
+// One block per (row, head): the parts' (max, sum, O) merged in the order of the parts, the sink added to the
+// denominator, the output written. A part without keys has max -inf and weighs nothing.
+__global__ void latent_merge_kernel(const float* __restrict__ scratch, const float* __restrict__ sink, bf16* __restrict__ out,
+                                    int out_stride, int H, int R, int parts) {
+  const int row = blockIdx.x, head = blockIdx.y;
+  const float* rec = scratch + (static_cast<size_t>(row) * H + head) * parts * (R + 2);
+  pdl_wait();
+  pdl_trigger();
+  float m_all = sink ? sink[head] * LF_LOG2E : -INFINITY;
+  for (int k = 0; k < parts; ++k) m_all = fmaxf(m_all, rec[static_cast<size_t>(k) * (R + 2)]);
+  float den = sink ? lf_exp2(sink[head] * LF_LOG2E - m_all) : 0.0f;
+  for (int k = 0; k < parts; ++k) {
+    const float m = rec[static_cast<size_t>(k) * (R + 2)];
+    if (m != -INFINITY) den += rec[static_cast<size_t>(k) * (R + 2) + 1] * lf_exp2(m - m_all);
+  }
+  bf16* orow = out + static_cast<size_t>(row) * out_stride + static_cast<size_t>(head) * R;
+  for (int d = threadIdx.x; d < R; d += blockDim.x) {
+    float acc = 0.0f;
+    for (int k = 0; k < parts; ++k) {
+      const float m = rec[static_cast<size_t>(k) * (R + 2)];
+      if (m != -INFINITY) acc = fmaf(rec[static_cast<size_t>(k) * (R + 2) + 2 + d], lf_exp2(m - m_all), acc);
+    }
+    orow[d] = __float2bfloat16_rn(acc / den);
+  }
+}
+
 }  // namespace dl
 
 // Shared memory a launch needs, for the host to check against the device's limit.
@@ -305,11 +362,15 @@ static size_t lf_smem_bytes(int R, int r) {
 
 // qw: [rows, H * (R + r)] wide queries; cache: [pages, page_size, R + r]; tiles: n_tiles x (slot, first row, rows,
 // first position), rows at most 32 / HG (HG = heads to a block: min(H, 32), or any divisor-free count up to 32);
-// out: [rows, H * R]. R, r: multiples of 8, R at most 512. sink may be null.
+// out: [rows, H * R]. R, r: multiples of 8, R at most 512. sink may be null. parts > 1: the keys of every tile are
+// dealt over that many blocks, through scratch (float32 [rows, H, parts, R + 2]; `rows` rows are merged afterwards).
 DL_EXPORT int dl_latent_attention_flash(const void* qw, int q_stride, const void* cache, const int* block_table, int max_blocks,
                                         const int* tiles, int n_tiles, const float* sink, void* out, int out_stride, int H, int R,
-                                        int r, int page_size, float scale, int window, int HG, cudaStream_t stream) {
+                                        int r, int page_size, float scale, int window, int HG, int parts, float* scratch,
+                                        int rows, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (parts < 1 || parts > 64 || (parts > 1 && (scratch == nullptr || rows <= 0 || (reinterpret_cast<uintptr_t>(scratch) & 7) != 0)))
+    return DL_ERR_UNSUPPORTED;
   if (H <= 0 || R <= 0 || R % 8 != 0 || r % 8 != 0 || r < 0 || R > 512 || page_size <= 0 || window < 0 || HG <= 0 || HG > 32 ||
       q_stride % 8 != 0 || out_stride % 2 != 0 || (reinterpret_cast<uintptr_t>(qw) & 15) != 0 ||
       (reinterpret_cast<uintptr_t>(cache) & 15) != 0 || (reinterpret_cast<uintptr_t>(out) & 3) != 0 ||
@@ -329,18 +390,24 @@ DL_EXPORT int dl_latent_attention_flash(const void* qw, int q_stride, const void
   p.out_stride = out_stride;
   p.H = H; p.R = R; p.r = r; p.page_size = page_size; p.window = window; p.HG = HG;
   p.scale = scale;
+  p.parts = parts;
+  p.scratch = scratch;
   const int groups = (H + HG - 1) / HG;
   if (groups > 65535) return DL_ERR_UNSUPPORTED;
-  dim3 grid(n_tiles, groups);
+  dim3 grid(n_tiles, groups, parts);
+  int code;
 #define DL_LAUNCH(NT)                                                                                                    \
   do {                                                                                                                   \
     cudaError_t e = cudaFuncSetAttribute(dl::latent_attention_flash_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                          static_cast<int>(smem));                                                        \
     if (e != cudaSuccess) return static_cast<int>(e);                                                                    \
-    return dl::launch_streaming(dl::latent_attention_flash_kernel<NT>, grid, dim3(dl::LF_THREADS), smem, stream, p);      \
+    code = dl::launch_streaming(dl::latent_attention_flash_kernel<NT>, grid, dim3(dl::LF_THREADS), smem, stream, p);      \
   } while (0)
   if (R <= 128) DL_LAUNCH(2);
-  if (R <= 256) DL_LAUNCH(4);
-  DL_LAUNCH(8);
+  else if (R <= 256) DL_LAUNCH(4);
+  else DL_LAUNCH(8);
 #undef DL_LAUNCH
+  if (code != 0 || parts == 1) return code;
+  return dl::launch_streaming(dl::latent_merge_kernel, dim3(rows, H), dim3(128), 0, stream, static_cast<const float*>(scratch), sink,
+                              static_cast<dl::bf16*>(out), out_stride, H, R, parts);
 }

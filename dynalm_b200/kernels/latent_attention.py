@@ -12,6 +12,7 @@ from __future__ import annotations
 import torch
 
 from . import ops
+from .device import sm_count
 
 UNITS = 32          # query units (row, head) to a block of the tensor-core kernel
 
@@ -61,7 +62,31 @@ def flash_applies(spec, dtype) -> bool:
             and ops.latent_flash_fits(spec.kv_rank, spec.rot_dim))
 
 
-def attend(wide: torch.Tensor, cache, ctx, out: torch.Tensor, spec, sink) -> bool:
+KEY_TILE = 64           # keys to a tile of the tensor-core kernel
+PART_ROWS = 64          # steps of single tokens up to this many rows may deal their keys over several blocks
+MAX_PARTS = 16
+
+
+def key_parts(ctx, spec, sms: int = 0) -> int:
+    """Into how many parts the keys of every query tile are dealt. Only steps in which every request brings one token,
+    and few of them: such a step has one block per request and group of heads, each walking all of its keys alone. The
+    count follows the step's longest span of keys in powers of two (cut off at the window), so that a growing context
+    keeps its launch shape, gives every part at least two key tiles, and aims at two blocks per SM."""
+    if not ctx.decode_only or ctx.num_tokens > PART_ROWS:
+        return 1
+    window = int(spec.get("window", 0))
+    span = 256
+    while span < ctx.max_kv_len:
+        span *= 2
+    if window > 0:
+        span = min(span, window)
+    tiles = span // KEY_TILE + 1
+    blocks = ctx.num_tokens * -(-spec.num_heads // heads_per_block(spec.num_heads))
+    want = -(-2 * (sms or sm_count()) // blocks)
+    return max(1, min(want, tiles // 2, MAX_PARTS))
+
+
+def attend(wide: torch.Tensor, cache, ctx, out: torch.Tensor, spec, sink, runtime=None) -> bool:
     """The tensor-core kernel over the step's tiles; False (nothing done) when it does not take this model or step."""
     if not flash_applies(spec, wide.dtype):
         return False
@@ -70,7 +95,12 @@ def attend(wide: torch.Tensor, cache, ctx, out: torch.Tensor, spec, sink) -> boo
         return False
     tiles, n_tiles = planned
     (records,) = cache.arrays
+    parts = key_parts(ctx, spec) if runtime is not None else 1
+    scratch = None
+    if parts > 1:
+        scratch = runtime.flat(f"latent_parts_{spec.num_heads}_{spec.kv_rank}",
+                               PART_ROWS * spec.num_heads * MAX_PARTS * (spec.kv_rank + 2))
     ops.latent_attention_flash(wide, records, cache.block_table, tiles, n_tiles, sink, out, spec.num_heads, spec.kv_rank,
                                spec.rot_dim, cache.page_size, float(spec.scale), int(spec.get("window", 0)),
-                               heads_per_block(spec.num_heads))
+                               heads_per_block(spec.num_heads), parts, scratch)
     return True

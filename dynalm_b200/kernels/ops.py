@@ -47,7 +47,7 @@ _SIGNATURES = {
     "head_linear_tc": {
         "dl_head_linear_tc": [_P, _I, _I, _I, _P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _P]},
     "latent_attention_flash": {
-        "dl_latent_attention_flash": [_P, _I, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P]},
+        "dl_latent_attention_flash": [_P, _I, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _I, _P]},
     "qk_norm_cache": {
         "dl_qk_norm_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _L, _I, _I, _P, _P, _F, _F, _I, _I, _I, _I, _I, _I,
                                    _I, _I, _P]},
@@ -798,10 +798,13 @@ def latent_flash_fits(kv_rank: int, rot_dim: int) -> bool:
 
 def latent_attention_flash(qw: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor,
                            n_tiles: int, sink: Optional[torch.Tensor], out: torch.Tensor, heads: int, kv_rank: int,
-                           rot_dim: int, page_size: int, scale: float, window: int, heads_per_block: int) -> None:
+                           rot_dim: int, page_size: int, scale: float, window: int, heads_per_block: int, parts: int = 1,
+                           scratch: Optional[torch.Tensor] = None) -> None:
     """latent_attention on bf16 tensor cores: one block per (query tile, group of `heads_per_block` heads), the tiles
     int32 [n_tiles, 4] = (request slot, first row, rows, first position) with at most 32 // heads_per_block rows each.
-    See csrc/latent_attention_flash.cu."""
+    parts > 1: the key tiles of every query tile are dealt over that many blocks, which leave their shares in `scratch`
+    (float32, rows * heads * parts * (kv_rank + 2) at least) for a merge kernel: for steps of few rows, which would
+    leave most of the GPU idle. See csrc/latent_attention_flash.cu."""
     _cuda(qw, cache, block_table, tiles, sink, out)
     _rows_contiguous(qw, "qw")
     _rows_contiguous(out, "out")
@@ -815,12 +818,18 @@ def latent_attention_flash(qw: torch.Tensor, cache: torch.Tensor, block_table: t
         raise InvalidArgument("latent_attention_flash: tiles int32 [n_tiles, 4]")
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != heads):
         raise InvalidArgument("latent_attention_flash: sinks float32 [heads]")
-    check_limits("latent_attention_flash", pages=cache.shape[0], requests=block_table.shape[0], rows=qw.shape[0])
+    rows = qw.shape[0]
+    if parts > 1 and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < rows * heads * parts * (kv_rank + 2)):
+        raise InvalidArgument("latent_attention_flash: scratch float32 [rows, heads, parts, kv_rank + 2]")
+    check_limits("latent_attention_flash", pages=cache.shape[0], requests=block_table.shape[0], rows=rows)
     _take_ahead()
     _check(_fn("latent_attention_flash", "dl_latent_attention_flash")(
         _p(qw), qw.stride(0), _p(cache), _p(block_table), block_table.stride(0), _p(tiles), n_tiles, _p(sink), _p(out),
-        out.stride(0), heads, kv_rank, rot_dim, page_size, scale, window, heads_per_block, _stream()),
-        "latent_attention_flash")
+        out.stride(0), heads, kv_rank, rot_dim, page_size, scale, window, heads_per_block, parts,
+        _p(scratch) if parts > 1 else None, rows, _stream()), "latent_attention_flash")
+    if parts > 1:
+        global LAUNCHES
+        LAUNCHES += 1
 
 
 def qk_norm_cache_write(qkv: torch.Tensor, positions: torch.Tensor, row_slot: torch.Tensor,

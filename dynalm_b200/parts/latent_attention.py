@@ -85,6 +85,10 @@ class LatentAttention:
         from ..kernels import latent_attention as fast
         return [fast.tile_plan(self.spec)] if fast.flash_applies(self.spec, self.rt.dtype) else []
 
+    def graph_key(self, ctx) -> tuple:
+        from ..kernels import latent_attention as fast
+        return (("latent_parts", fast.key_parts(ctx, self.spec)),) if fast.flash_applies(self.spec, self.rt.dtype) else ()
+
     def cache_spec(self) -> Optional[CacheSpec]:
         s = self.spec
         return CacheSpec(kind="pages", entry_shape=(s.kv_rank + s.rot_dim,), tensors=1, window=int(s.get("window", 0)))
@@ -119,7 +123,7 @@ class LatentAttention:
         s = self.spec
         (records,) = cache.arrays
         from ..kernels import latent_attention as fast
-        if fast.attend(wide, cache, ctx, out, s, self.sink):
+        if fast.attend(wide, cache, ctx, out, s, self.sink, self.rt):
             return
         ops.latent_attention(wide, records, cache.block_table, ctx.positions, ctx.row_slot, self.sink, out, s.num_heads,
                              s.kv_rank, s.rot_dim, cache.page_size, float(s.scale), int(s.get("window", 0)))

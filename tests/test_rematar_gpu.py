@@ -479,15 +479,25 @@ def test_tensor_core_attention_over_tiles_of_a_step(H, R, r, window):
     tiles = torch.from_numpy(host).to(DEV)
     out = torch.zeros(n, H * R, dtype=dtype, device=DEV)
     ops.latent_attention_flash(q_t, cache, table, tiles, n_tiles, sink, out, H, R, r, page, scale, window, fast.heads_per_block(H))
-    got = _np(out).reshape(n, H, R)
     qf = _np(q_t).reshape(n, H, R + r)
-    for h in range(H):
-        wts = plain.window_sink_softmax((qf[:, h] @ rec.T) * scale, np.asarray(positions), np.arange(n_keys), window,
-                                        float(sink[h]))
-        want = wts @ rec[:, :R]
-        err = np.abs(got[:, h] - want).max(axis=1)
-        bad = int(err.argmax())
-        assert err[bad] <= 3e-2 * max(1.0, np.abs(want).max()), f"head {h}, query at {positions[bad]}: {err[bad]:.3g}"
+    want = [plain.window_sink_softmax((qf[:, h] @ rec.T) * scale, np.asarray(positions), np.arange(n_keys), window,
+                                      float(sink[h])) @ rec[:, :R] for h in range(H)]
+
+    def check(what):
+        got = _np(out).reshape(n, H, R)
+        for h in range(H):
+            err = np.abs(got[:, h] - want[h]).max(axis=1)
+            bad = int(err.argmax())
+            assert err[bad] <= 3e-2 * max(1.0, np.abs(want[h]).max()), f"{what}: head {h}, query at {positions[bad]}: {err[bad]:.3g}"
+
+    check("one block per tile")
+    # the keys of every tile dealt over several blocks (more parts than some tiles have key tiles), merged afterwards
+    for parts in (2, 5, 16):
+        out.fill_(7.0)
+        scratch = torch.full((n * H * parts * (R + 2),), float("nan"), device=DEV)
+        ops.latent_attention_flash(q_t, cache, table, tiles, n_tiles, sink, out, H, R, r, page, scale, window,
+                                   fast.heads_per_block(H), parts, scratch)
+        check(f"{parts} parts")
 
 
 # ---------------------------------------------------------------------------------------------
