@@ -38,7 +38,7 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-enum { SK_OUT_BF16 = 0, SK_OUT_F32 = 1, SK_OUT_SWIGLU = 2, SK_OUT_ARGMAX = 3, SK_OUT_RELU2 = 4 };
+enum { SK_OUT_BF16 = 0, SK_OUT_F32 = 1, SK_OUT_SWIGLU = 2, SK_OUT_ARGMAX = 3, SK_OUT_RELU2 = 4, SK_OUT_GELU = 5 };
 
 // The weight stream of one block: y^T tile = W rows (wrow, 16 * MT of them in MMA row order) times x^T, k-blocks
 // [blk_begin, blk_end) dealt to the warps round-robin. Leaves every warp's partial tile in `red`
@@ -237,6 +237,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
       if (mode == SK_OUT_RELU2) {        // the squared ReLU of an ungated feed-forward
         v = fmaxf(v, 0.0f);
         v *= v;
+      } else if (mode == SK_OUT_GELU) {  // or its GELU in the tanh form
+        v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
       }
       static_cast<bf16*>(y)[static_cast<size_t>(b) * ldy + f] = __float2bfloat16_rn(v);
     }
@@ -346,7 +348,7 @@ DL_EXPORT int dl_gemm_skinny(const void* x, int ldx, const void* w, void* y, int
                              long long ahead_bytes, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64 || K <= 0 || (K & 7) || (ldx & 7) || n_split < 1 || n_split > 64 || (n_split > 1 && mode != dl::SK_OUT_F32) ||
-      (mode == dl::SK_OUT_SWIGLU && (N & 1)) || mode < 0 || mode > 4 || (mode == dl::SK_OUT_ARGMAX && !(out_scale > 0.0f)))
+      (mode == dl::SK_OUT_SWIGLU && (N & 1)) || mode < 0 || mode > 5 || (mode == dl::SK_OUT_ARGMAX && !(out_scale > 0.0f)))
     return DL_ERR_UNSUPPORTED;
   if (M <= 8) return dl::launch_skinny<1, 1>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, ahead, ahead_bytes, stream);
   if (M <= 16) return dl::launch_skinny<1, 2>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, ahead, ahead_bytes, stream);

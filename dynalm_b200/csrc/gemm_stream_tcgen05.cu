@@ -30,7 +30,7 @@ constexpr int GS_BM = 128;                 // features per tile
 constexpr int GS_BK = 64;                  // 64 bf16 = 128 bytes: one swizzle row
 constexpr int GS_THREADS = 192;
 constexpr uint32_t GS_A_BYTES = GS_BM * GS_BK * 2;
-enum { GS_OUT_BF16 = 0, GS_OUT_F32 = 1, GS_OUT_SWIGLU = 2, GS_OUT_RELU2 = 3 };
+enum { GS_OUT_BF16 = 0, GS_OUT_F32 = 1, GS_OUT_SWIGLU = 2, GS_OUT_RELU2 = 3, GS_OUT_GELU = 4 };
 enum { GS_ERR_PRODUCER = 21, GS_ERR_MMA = 22, GS_ERR_EPILOGUE = 23 };
 
 template <int NB> struct GS {
@@ -182,7 +182,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[c0 + j] = __uint_as_float(v[j]);
       }
-      if (mode == GS_OUT_BF16 || mode == GS_OUT_F32 || mode == GS_OUT_RELU2) {
+      if (mode == GS_OUT_BF16 || mode == GS_OUT_F32 || mode == GS_OUT_RELU2 || mode == GS_OUT_GELU) {
         const int f = f0 + fl;
         if (f < N) {
           if (mode == GS_OUT_F32) {
@@ -199,6 +199,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (mode == GS_OUT_RELU2) {      // the squared ReLU of an ungated feed-forward
                   v = fmaxf(v, 0.0f);
                   v *= v;
+                } else if (mode == GS_OUT_GELU) {  // or its GELU in the tanh form
+                  v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
                 }
                 out[static_cast<size_t>(b) * ldy] = __float2bfloat16_rn(v);
               }
@@ -302,6 +304,6 @@ static int gs_run(const void* x, int ldx, const void* w, void* y, int ldy, int M
 // status: one device int, set to a nonzero code if a wait inside the kernel timed out (left untouched otherwise).
 DL_EXPORT int dl_gemm_stream(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode,
                              float out_scale, int n_split, long long split_stride, int* status, cudaStream_t stream) {
-  if (mode < 0 || mode > 3) return DL_ERR_UNSUPPORTED;     // 3: y bf16 [M, N] = max(x W^T, 0)^2
+  if (mode < 0 || mode > 4) return DL_ERR_UNSUPPORTED;     // 3: y bf16 [M, N] = max(x W^T, 0)^2; 4: = gelu_tanh(x W^T)
   return dl::gs_run(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, status, stream);
 }

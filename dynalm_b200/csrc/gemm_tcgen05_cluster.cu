@@ -36,7 +36,7 @@ struct T5Pair {
 // As dl_gemm_tcgen05.
 DL_EXPORT int dl_gemm_tcgen05_cluster(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode,
                                       float out_scale, int* status, cudaStream_t stream) {
-  if (mode < 0 || (mode > 2 && mode != dl::T5_OUT_RELU2)) return DL_ERR_UNSUPPORTED;
+  if (mode < 0 || (mode > 2 && mode != dl::T5_OUT_RELU2 && mode != dl::T5_OUT_GELU)) return DL_ERR_UNSUPPORTED;
   const dl::QkvRope none = {};
   return t5_launch<dl::T5Pair>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, status, none, stream);
 }

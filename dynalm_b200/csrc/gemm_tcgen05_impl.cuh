@@ -23,7 +23,7 @@ template <int BN> struct T5 {
   static constexpr size_t SMEM = static_cast<size_t>(STAGES) * STAGE_BYTES + T5_STORE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
 
-enum { T5_OUT_BF16 = 0, T5_OUT_F32 = 1, T5_OUT_SWIGLU = 2, T5_OUT_QKV_ROPE = 3, T5_OUT_RELU2 = 4 };
+enum { T5_OUT_BF16 = 0, T5_OUT_F32 = 1, T5_OUT_SWIGLU = 2, T5_OUT_QKV_ROPE = 3, T5_OUT_RELU2 = 4, T5_OUT_GELU = 5 };
 enum { T5_ERR_PRODUCER = 1, T5_ERR_MMA = 2, T5_ERR_EPILOGUE = 3 };
 
 // Which output tile a tile number stands for. Tiles are numbered in groups of `group_m` row blocks: inside a
@@ -337,12 +337,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             }
           } else {
             // bf16 out; with T5_OUT_RELU2 the squared ReLU of an ungated feed-forward on the way
-            const bool relu2 = mode == T5_OUT_RELU2;
+            // (T5_OUT_GELU: its GELU in the tanh form)
+            const bool relu2 = mode == T5_OUT_RELU2, gelu = mode == T5_OUT_GELU;
             auto fin = [&](uint32_t u) {
               float x = __uint_as_float(u) * out_scale;
               if (relu2) {
                 x = fmaxf(x, 0.0f);
                 x *= x;
+              } else if (gelu) {
+                x = 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
               }
               return x;
             };
@@ -395,14 +398,14 @@ static inline int make_map(CUtensorMap* map, const void* base, int rows, int col
 
 // x: bf16 [M, K] rows of ldx elements; w: bf16 [N, K] contiguous; both 16-byte aligned with K and ldx multiples of 8.
 // mode 0: y bf16 [M, N] (N % 8 == 0); mode 1: y fp32 [M, N] (N % 4 == 0); mode 2: w = [gate; up] with N = 2F rows,
-// y bf16 [M, F] = silu(x Wg^T) * (x Wu^T) (F % 8 == 0); mode 4: y bf16 [M, N] = max(x W^T, 0)^2. status: one device int, set to a nonzero code if a wait
+// y bf16 [M, F] = silu(x Wg^T) * (x Wu^T) (F % 8 == 0); mode 4: y bf16 [M, N] = max(x W^T, 0)^2; mode 5: = gelu_tanh(x W^T). status: one device int, set to a nonzero code if a wait
 // inside the kernel timed out (left untouched otherwise).
 template <class P>
 static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode, float out_scale,
                      int* status, const dl::QkvRope& rope, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
-      status == nullptr || mode < 0 || mode > 4)
+      status == nullptr || mode < 0 || mode > 5)
     return DL_ERR_UNSUPPORTED;
   const int feats = mode == dl::T5_OUT_SWIGLU ? N / 2 : N;
   if ((mode == dl::T5_OUT_SWIGLU && (N & 1)) || (mode == dl::T5_OUT_F32 ? (feats & 3) || (ldy & 3) : (feats & 7) || (ldy & 7)) ||

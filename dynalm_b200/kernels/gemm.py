@@ -175,34 +175,27 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, runtime, inner: int)
 
 
 def linear_act(x: torch.Tensor, w_up: torch.Tensor, runtime, inner: int, activation: str) -> torch.Tensor:
-    """act(x W^T), the first half of an ungated feed-forward, for the activations the kernels have: "relu2" sits in
-    the product's epilogue where it can (linear_relu2); "gelu_tanh" follows the product as a kernel of its own."""
-    if activation == "relu2":
-        return linear_relu2(x, w_up, runtime, inner)
-    act = runtime.buffer("ffn_act", (x.shape[0], inner))
-    linear(x, w_up, act)
-    if activation == "gelu_tanh":
-        ops.gelu_tanh(act, act)
-    else:
+    """act(x W^T), the first half of an ungated feed-forward, act = "relu2" (max(z, 0)^2) or "gelu_tanh": the
+    activation sits in the product's epilogue wherever one of this package's bfloat16 kernels runs the product, else
+    the product is followed by the activation kernel (float32, and the few shapes that go to the library)."""
+    if activation not in ("relu2", "gelu_tanh"):
         raise ValueError(f"no kernel for activation '{activation}'")
+    rows = x.shape[0]
+    act = runtime.buffer("ffn_act", (rows, inner))
+    if x.dtype == torch.bfloat16 and use_stream(x, w_up):
+        ops.gemm_stream(x, w_up, act, activation)
+        return act
+    if x.dtype == torch.bfloat16 and skinny_ok(x, w_up):
+        ops.gemm_skinny(x, w_up, act, activation)
+        return act
+    if x.dtype == torch.bfloat16 and tcgen05_ok(x, w_up, act, inner):
+        ops.gemm_tcgen05(x, w_up, act, activation)
+        return act
+    linear(x, w_up, act)
+    (ops.relu2 if activation == "relu2" else ops.gelu_tanh)(act, act)
     return act
 
 
 def linear_relu2(x: torch.Tensor, w_up: torch.Tensor, runtime, inner: int) -> torch.Tensor:
-    """max(x W^T, 0)^2, the first half of an ungated feed-forward: the activation sits in the product's epilogue
-    wherever one of this package's bfloat16 kernels runs the product, else the product is followed by the
-    activation kernel (float32, and the few shapes that go to the library)."""
-    rows = x.shape[0]
-    act = runtime.buffer("ffn_act", (rows, inner))
-    if x.dtype == torch.bfloat16 and use_stream(x, w_up):
-        ops.gemm_stream(x, w_up, act, "relu2")
-        return act
-    if x.dtype == torch.bfloat16 and skinny_ok(x, w_up):
-        ops.gemm_skinny(x, w_up, act, "relu2")
-        return act
-    if x.dtype == torch.bfloat16 and tcgen05_ok(x, w_up, act, inner):
-        ops.gemm_tcgen05(x, w_up, act, "relu2")
-        return act
-    linear(x, w_up, act)
-    ops.relu2(act, act)
-    return act
+    """max(x W^T, 0)^2 (see linear_act)."""
+    return linear_act(x, w_up, runtime, inner, "relu2")

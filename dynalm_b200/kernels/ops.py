@@ -1313,8 +1313,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str =
     N = w.shape[0]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or w.shape[1] != K:
         raise InvalidArgument("gemm_skinny: x and w bfloat16, w [N, K] contiguous")
-    if mode == "relu2" and (out.dim() != 2 or out.dtype != torch.bfloat16):
-        raise InvalidArgument("gemm_skinny: relu2 needs out [M, N] bfloat16")
+    if mode in ("relu2", "gelu_tanh") and (out.dim() != 2 or out.dtype != torch.bfloat16):
+        raise InvalidArgument("gemm_skinny: an activation needs out [M, N] bfloat16")
     if M > SKINNY_MAX_ROWS or K % 8 or x.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
         raise Unsupported(f"gemm_skinny: at most {SKINNY_MAX_ROWS} rows, K a multiple of 8, 16-byte aligned rows")
     n_split, split_stride = 1, 0
@@ -1330,8 +1330,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str =
         if out.shape != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
             raise InvalidArgument("gemm_skinny: out [M, N] bfloat16 or float32")
         code, ldy = (0 if out.dtype == torch.bfloat16 else 1), out.stride(0)
-        if mode == "relu2":
-            code = 4
+        if mode in ("relu2", "gelu_tanh"):
+            code = 4 if mode == "relu2" else 5
     ahead, ahead_bytes = _take_ahead()
     _check(_fn("gemm_skinny", "dl_gemm_skinny")(_p(x), x.stride(0), _p(w), _p(out), ldy, M, N, K, code, out_scale,
                                                  n_split, split_stride, ahead, ahead_bytes, _stream()), "gemm_skinny")
@@ -1360,8 +1360,8 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str 
         if out.dtype == torch.bfloat16:
             if N % 8 or out.stride(0) % 8:
                 raise Unsupported("gemm_tcgen05: bfloat16 output needs N and its row pitch to be multiples of 8")
-            code = 4 if mode == "relu2" else 0
-        elif out.dtype == torch.float32 and mode != "relu2":
+            code = 4 if mode == "relu2" else (5 if mode == "gelu_tanh" else 0)
+        elif out.dtype == torch.float32 and mode not in ("relu2", "gelu_tanh"):
             if N % 4 or out.stride(0) % 4:
                 raise Unsupported("gemm_tcgen05: float32 output needs N and its row pitch to be multiples of 4")
             code = 1
@@ -1415,10 +1415,10 @@ def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str =
         if out.shape != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
             raise InvalidArgument("gemm_stream: out [M, N] bfloat16 or float32")
         code, ldy = (0 if out.dtype == torch.bfloat16 else 1), out.stride(0)
-        if mode == "relu2":
+        if mode in ("relu2", "gelu_tanh"):
             if out.dtype != torch.bfloat16:
-                raise InvalidArgument("gemm_stream: relu2 needs out [M, N] bfloat16")
-            code = 3
+                raise InvalidArgument("gemm_stream: an activation needs out [M, N] bfloat16")
+            code = 3 if mode == "relu2" else 4
     _check(_fn("gemm_stream_tcgen05", "dl_gemm_stream")(
         _p(x), x.stride(0), _p(w), _p(out), ldy, M, N, K, code, out_scale, n_split, split_stride,
         _p(_status_word(x.device)), _stream()), "gemm_stream")

@@ -96,6 +96,21 @@ def test_norm_after_the_sum(dtype):
                 assert torch.equal(out, got_x.to(torch.bfloat16))        # the copy is the stream, rounded once
 
 
+@pytest.mark.parametrize("rows,inner,width", [(4, 272, 256), (12, 272, 256), (40, 272, 256), (1024, 2048, 256), (300, 4096, 512)])
+def test_gelu_in_the_epilogue_of_every_product_kernel(rows, inner, width):
+    """gelu_tanh(x W^T) by whichever kernel the dispatcher picks for the shape (few rows: the weight-streaming ones; many
+    tiles: the tcgen05 one; in between the library followed by the activation kernel) against the plain product."""
+    from dynalm_b200.engine.runtime import Runtime
+    from dynalm_b200.kernels.gemm import linear_act
+    rng = np.random.RandomState(rows)
+    rt = Runtime(DEV, torch.bfloat16, max_tokens=1024)
+    x = _t(rng.randn(rows, width), torch.bfloat16)
+    w = _t(rng.randn(inner, width) * 0.1, torch.bfloat16)
+    got = _np(linear_act(x, w, rt, inner, "gelu_tanh"))
+    want = plain.gelu_tanh(_np(x) @ _np(w).T)
+    assert np.abs(got - want).max() <= 1e-2 * max(1.0, np.abs(want).max())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rows", [1, 5, 40, 300])
 def test_gelu_feed_forward(dtype, rows):
@@ -130,13 +145,13 @@ def _step_arrays(portions, slots):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("taps,channels", [(4, 40), (2, 7), (1, 16), (5, 300)])
-def test_convolution_in_portions_carries_its_last_inputs(dtype, taps, channels):
+@pytest.mark.parametrize("taps,channels,col0", [(4, 40, 3), (2, 7, 3), (1, 16, 3), (5, 300, 3), (4, 48, 8), (3, 64, 16)])
+def test_convolution_in_portions_carries_its_last_inputs(dtype, taps, channels, col0):
     """Two requests in slots 2 and 0, cut differently (portions shorter than, equal to and longer than the taps),
     side by side in one batch; then slot 2 is used again by a new request and must not see the old inputs."""
     from dynalm_b200.kernels import ops
     rng = np.random.RandomState(taps * 100 + channels)
-    col0, extra = 3, 2
+    extra = 2 if col0 % 8 else 8                                               # (pitches in multiples of 8 take 16-byte loads)
     w, b = _t(rng.randn(channels, taps)), _t(rng.randn(channels))
     keep_off = 11
     state = torch.zeros(4, keep_off + (taps - 1) * channels + 5, device=DEV)
