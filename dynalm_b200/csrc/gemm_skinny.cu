@@ -238,7 +238,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
         v = fmaxf(v, 0.0f);
         v *= v;
       } else if (mode == SK_OUT_GELU) {  // or its GELU in the tanh form
-        v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        v = gelu_tanh_bf16(v);
       }
       static_cast<bf16*>(y)[static_cast<size_t>(b) * ldy + f] = __float2bfloat16_rn(v);
     }

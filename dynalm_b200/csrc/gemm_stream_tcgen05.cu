@@ -200,7 +200,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                   v = fmaxf(v, 0.0f);
                   v *= v;
                 } else if (mode == GS_OUT_GELU) {  // or its GELU in the tanh form
-                  v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+                  v = gelu_tanh_bf16(v);
                 }
                 out[static_cast<size_t>(b) * ldy] = __float2bfloat16_rn(v);
               }

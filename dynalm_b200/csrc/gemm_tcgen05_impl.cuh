@@ -345,7 +345,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 x = fmaxf(x, 0.0f);
                 x *= x;
               } else if (gelu) {
-                x = 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+                x = gelu_tanh_bf16(x);
               }
               return x;
             };

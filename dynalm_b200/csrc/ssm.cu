@@ -41,7 +41,7 @@ __global__ void ssm_conv_kernel(const T* __restrict__ proj, int proj_stride, int
     float v;
     if (p >= first) v = to_float(proj[static_cast<size_t>(row - k) * proj_stride + col0 + ch]);
     else v = kept[static_cast<size_t>(K - 1 - (first - p)) * channels + ch];
-    acc = fmaf(taps[static_cast<size_t>(ch) * K + (K - 1 - k)], v, acc);
+    acc = fmaf(taps[static_cast<size_t>(K - 1 - k) * channels + ch], v, acc);
   }
   out[idx] = from_float<T>(silu_f(acc));
 }
@@ -76,8 +76,9 @@ __global__ void ssm_conv_vec_kernel(const T* __restrict__ proj, int proj_stride,
 #pragma unroll
       for (int j = 0; j < V; ++j) v[j] = kr[j];
     }
+    const float* tk = taps + static_cast<size_t>(K - 1 - k) * channels + ch;
 #pragma unroll
-    for (int j = 0; j < V; ++j) acc[j] = fmaf(taps[static_cast<size_t>(ch + j) * K + (K - 1 - k)], v[j], acc[j]);
+    for (int j = 0; j < V; ++j) acc[j] = fmaf(tk[j], v[j], acc[j]);
   }
 #pragma unroll
   for (int j = 0; j < V; ++j) acc[j] = silu_f(acc[j]);
@@ -275,8 +276,9 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __
 
 }  // namespace dl
 
-// out[row, ch] = silu(bias[ch] + sum_k taps[ch, k] * input(row's position - (K - 1 - k), ch)), the inputs being
-// columns col0 .. col0 + channels of proj. state: [slots, state_stride] float32, a slot's kept inputs at keep_off.
+// out[row, ch] = silu(bias[ch] + sum_k taps[k, ch] * input(row's position - (K - 1 - k), ch)), the inputs being
+// columns col0 .. col0 + channels of proj; taps: float32 [K, channels], tap by tap (the model file's [channels, K]
+// transposed, so that neighbouring channels read neighbouring words). state: [slots, state_stride] float32, a slot's kept inputs at keep_off.
 DL_EXPORT int dl_ssm_conv(int dtype, const void* proj, int proj_stride, int col0, int channels, const float* taps,
                           const float* bias, int K, const float* state, long long state_stride, long long keep_off,
                           const int* positions, const int* row_request, const int* row_slot, const int* pos_start,

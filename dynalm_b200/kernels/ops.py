@@ -549,20 +549,21 @@ def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
     _check(_fn("norm_after_sum", "dl_cast_rows")(dtype_code(out.dtype), _p(x), _p(out), x.numel(), _stream()), "cast_rows")
 
 
-def ssm_conv(proj: torch.Tensor, col0: int, channels: int, taps: torch.Tensor, bias: Optional[torch.Tensor],
+def ssm_conv(proj: torch.Tensor, col0: int, channels: int, taps_t: torch.Tensor, bias: Optional[torch.Tensor],
              state: torch.Tensor, keep_off: int, positions: torch.Tensor, row_request: torch.Tensor,
              row_slot: torch.Tensor, pos_start: torch.Tensor, out: torch.Tensor) -> None:
-    """out[row, ch] = silu(bias[ch] + sum_k taps[ch, k] * u(position - (K - 1 - k), ch)), u = columns col0 .. col0 +
-    channels of proj; inputs in front of a request's first row of the step come from its kept inputs, state[slot,
-    keep_off + j * channels + ch] (oldest first). taps: float32 [channels, K]; state: float32 [slots, n]. See
-    csrc/ssm.cu."""
+    """out[row, ch] = silu(bias[ch] + sum_k taps_t[k, ch] * u(position - (K - 1 - k), ch)), u = columns col0 .. col0 +
+    channels of proj (the last tap is the current token's); inputs in front of a request's first row of the step come
+    from its kept inputs, state[slot, keep_off + j * channels + ch] (oldest first). taps_t: float32 [K, channels],
+    tap by tap; state: float32 [slots, n]. See csrc/ssm.cu."""
+    taps = taps_t
     _cuda(proj, taps, bias, state, positions, row_request, row_slot, pos_start, out)
     _rows_contiguous(proj, "proj")
     rows = proj.shape[0]
-    K = taps.shape[1]
-    if taps.dtype != torch.float32 or not taps.is_contiguous() or taps.shape[0] != channels \
+    K = taps.shape[0]
+    if taps.dtype != torch.float32 or not taps.is_contiguous() or taps.dim() != 2 or taps.shape[1] != channels \
             or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != channels)):
-        raise InvalidArgument("ssm_conv: taps float32 [channels, K] and bias float32 [channels]")
+        raise InvalidArgument("ssm_conv: taps float32 [K, channels] and bias float32 [channels]")
     if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or keep_off + (K - 1) * channels > state.shape[1]:
         raise InvalidArgument("ssm_conv: state float32 [slots, n] with room for the kept inputs")
     if out.dtype != proj.dtype or out.shape != (rows, channels) or not out.is_contiguous() or col0 + channels > proj.shape[1]:

@@ -60,7 +60,7 @@ class StateSpaceMixer:
         self.inner = H * P
         self.channels = self.inner + 2 * G * N
         self.w_in = tensors["in_proj"]
-        self.taps = tensors["conv"].contiguous()
+        self.taps = tensors["conv"].t().contiguous()          # [taps, channels]: neighbouring channels in neighbouring words
         self.conv_bias = tensors["conv_bias"]
         self.dt_bias, self.a_log, self.d = tensors["dt_bias"], tensors["a_log"], tensors["d"]
         self.norm = tensors["norm"]

@@ -170,7 +170,7 @@ def test_convolution_in_portions_carries_its_last_inputs(dtype, taps, channels, 
             r0 += n
         pos, rreq, rslot, q_start, pos_start, slots = _step_arrays([(f, n) for _, f, n in batch], [s for s, _, _ in batch])
         out = torch.zeros(rows, channels, dtype=dtype, device=DEV)
-        ops.ssm_conv(proj, col0, channels, w, b, state, keep_off, pos, rreq, rslot, pos_start, out)
+        ops.ssm_conv(proj, col0, channels, w.t().contiguous(), b, state, keep_off, pos, rreq, rslot, pos_start, out)
         ops.ssm_conv_keep(proj, col0, channels, taps, state, keep_off, q_start, slots, len(batch))
         r0 = 0
         tol = 1e-5 if dtype == torch.float32 else 2e-2
@@ -190,7 +190,7 @@ def test_convolution_in_portions_carries_its_last_inputs(dtype, taps, channels, 
     proj[:, col0:col0 + channels] = _t(fresh, dtype)
     pos, rreq, rslot, q_start, pos_start, slots = _step_arrays([(0, 3)], [2])
     out = torch.zeros(3, channels, dtype=dtype, device=DEV)
-    ops.ssm_conv(proj, col0, channels, w, b, state, keep_off, pos, rreq, rslot, pos_start, out)
+    ops.ssm_conv(proj, col0, channels, w.t().contiguous(), b, state, keep_off, pos, rreq, rslot, pos_start, out)
     ref = plain.silu(plain.causal_conv(_np(_t(fresh, dtype)), _np(w), _np(b)))
     assert np.abs(_np(out) - ref).max() <= (1e-5 if dtype == torch.float32 else 2e-2) * max(1.0, np.abs(ref).max())
 
