@@ -121,7 +121,15 @@ __global__ void ssm_conv_keep_kernel(const T* __restrict__ proj, int proj_stride
 constexpr int SCAN_TT = 16;
 constexpr int SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_FINISH = 2;
 
-template <typename T, int NR, int MODE, bool FULL>
+__device__ __forceinline__ void scan_cp16(void* smem, const void* gmem) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+
+// ASYNC: the next tile's x, B and C are copied, as stored, into a second set of shared-memory buffers (cp.async, 16 bytes
+// a piece) while the current tile is computed, and its step sizes wait in registers; a tile then begins by widening
+// what has arrived. For sizes that 16-byte pieces fit (see the launch).
+template <typename T, int NR, int MODE, bool FULL, bool ASYNC>
 __global__ void __launch_bounds__(256, 3) ssm_scan_kernel(const T* __restrict__ u, int u_stride,            // [rows, H*P + 2*G*N] after the convolution
                                 const T* __restrict__ proj, int proj_stride, int dt_col,   // dt of head h at proj[row, dt_col + h]
                                 const float* __restrict__ dt_bias, const float* __restrict__ a_log,
@@ -163,23 +171,65 @@ __global__ void __launch_bounds__(256, 3) ssm_scan_kernel(const T* __restrict__ 
   for (int i = 0; i < NR; ++i)
     s[i] = (MODE != SCAN_LOCAL && live && (FULL || n_first + i < N)) ? S[static_cast<size_t>(n_first + i) * P + p] : 0.0f;
   float run_decay = 1.0f;
+  // (ASYNC) raw copies of a tile: [2 stages][B: TT x N | C: TT x N | x: TT x PV] of T
+  T* raw = reinterpret_cast<T*>(sDa + SCAN_TT);
+  const int raw_stage = SCAN_TT * (2 * N + PV);
+  float dt_raw = 0.0f;                          // this thread's token's step size of the tile at hand (threads < TT)
+  auto prefetch = [&](int t0, int stage) {
+    constexpr int V = PerVec<T>::n;
+    const int tt = min(SCAN_TT, n_tok - t0);
+    T* rs = raw + static_cast<size_t>(stage) * raw_stage;
+    const int nb = N / V, per = 2 * nb + PV / V;
+    for (int i = tid; i < tt * per; i += blockDim.x) {
+      const int t = i / per, c = i % per;
+      const T* row = u + static_cast<size_t>(r0 + t0 + t) * u_stride;
+      if (c < nb) scan_cp16(rs + t * N + c * V, row + inner + g * N + c * V);
+      else if (c < 2 * nb) scan_cp16(rs + (SCAN_TT + t) * N + (c - nb) * V, row + inner + (G + g) * N + (c - nb) * V);
+      else scan_cp16(rs + 2 * SCAN_TT * N + t * PV + (c - 2 * nb) * V, row + h * P + p0 + (c - 2 * nb) * V);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  if (ASYNC && n_tok > 0) {
+    prefetch(0, 0);
+    if (tid < min(SCAN_TT, n_tok)) dt_raw = to_float(proj[static_cast<size_t>(r0 + tid) * proj_stride + dt_col + h]);
+  }
   for (int t0 = 0; t0 < n_tok; t0 += SCAN_TT) {
     const int tt = min(SCAN_TT, n_tok - t0);
-    __syncthreads();                            // the tile before has been read
-    for (int i = tid; i < tt * N; i += blockDim.x) {
-      const int t = i / N, n = i % N;
-      const T* ur = u + static_cast<size_t>(r0 + t0 + t) * u_stride + inner + g * N + n;
-      sBC[i] = make_float2(to_float(ur[0]), to_float(ur[G * N]));
-    }
-    for (int i = tid; i < tt * PV; i += blockDim.x) {
-      const int t = i / PV, q = p0 + i % PV;
-      sX[i] = q < P ? to_float(u[static_cast<size_t>(r0 + t0 + t) * u_stride + h * P + q]) : 0.0f;
-    }
-    for (int t = tid; t < tt; t += blockDim.x) {
-      const float raw = to_float(proj[static_cast<size_t>(r0 + t0 + t) * proj_stride + dt_col + h]);
-      const float dt = softplus_f(raw + bias);
-      sDt[t] = dt;
-      sDa[t] = expf(-rate * dt);
+    if (ASYNC) asm volatile("cp.async.wait_group 0;\n" ::);
+    __syncthreads();                            // the tile before has been read (ASYNC: and this tile's copies are here)
+    if (ASYNC) {
+      const int stage = (t0 / SCAN_TT) & 1;
+      float dt_next = 0.0f;
+      if (t0 + SCAN_TT < n_tok) {
+        prefetch(t0 + SCAN_TT, stage ^ 1);
+        if (tid < min(SCAN_TT, n_tok - t0 - SCAN_TT))
+          dt_next = to_float(proj[static_cast<size_t>(r0 + t0 + SCAN_TT + tid) * proj_stride + dt_col + h]);
+      }
+      const T* rs = raw + static_cast<size_t>(stage) * raw_stage;
+      for (int i = tid; i < tt * N; i += blockDim.x) sBC[i] = make_float2(to_float(rs[i]), to_float(rs[SCAN_TT * N + i]));
+      for (int i = tid; i < tt * PV; i += blockDim.x) sX[i] = to_float(rs[2 * SCAN_TT * N + i]);
+      if (tid < tt) {
+        const float dt = softplus_f(dt_raw + bias);
+        sDt[tid] = dt;
+        sDa[tid] = expf(-rate * dt);
+      }
+      dt_raw = dt_next;
+    } else {
+      for (int i = tid; i < tt * N; i += blockDim.x) {
+        const int t = i / N, n = i % N;
+        const T* ur = u + static_cast<size_t>(r0 + t0 + t) * u_stride + inner + g * N + n;
+        sBC[i] = make_float2(to_float(ur[0]), to_float(ur[G * N]));
+      }
+      for (int i = tid; i < tt * PV; i += blockDim.x) {
+        const int t = i / PV, q = p0 + i % PV;
+        sX[i] = q < P ? to_float(u[static_cast<size_t>(r0 + t0 + t) * u_stride + h * P + q]) : 0.0f;
+      }
+      for (int t = tid; t < tt; t += blockDim.x) {
+        const float rawv = to_float(proj[static_cast<size_t>(r0 + t0 + t) * proj_stride + dt_col + h]);
+        const float dt = softplus_f(rawv + bias);
+        sDt[t] = dt;
+        sDa[t] = expf(-rate * dt);
+      }
     }
     __syncthreads();
     for (int t = 0; t < tt; ++t) {
@@ -347,13 +397,23 @@ DL_EXPORT int dl_ssm_scan(int dtype, const void* u, int u_stride, const void* pr
   const int slices = (P + PV - 1) / PV;
   if (slices > 65535) return DL_ERR_UNSUPPORTED;
   const int threads = PV * NS;
-  const size_t smem = sizeof(float) * (static_cast<size_t>(dl::SCAN_TT) * (2 * N + PV + NS * PV) + 2 * dl::SCAN_TT);
+  // 16-byte pieces fit: the next tile is copied while this one is computed
+  const int vec = dtype == 0 ? 4 : 8;
+  const bool async = N % vec == 0 && PV % vec == 0 && P % PV == 0 && u_stride % vec == 0 && threads >= dl::SCAN_TT &&
+                     (reinterpret_cast<uintptr_t>(u) & 15) == 0;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(dl::SCAN_TT) * (2 * N + PV + NS * PV) + 2 * dl::SCAN_TT) +
+                      (async ? 2 * static_cast<size_t>(dl::SCAN_TT) * (2 * N + PV) * (dtype == 0 ? 4 : 2) : 0);
   if (smem > 200 * 1024) return DL_ERR_UNSUPPORTED;
 #define DL_LAUNCH(T, R, MODE, F, BLOCKS)                                                                              \
   do {                                                                                                                \
+    if (async) DL_LAUNCH2(T, R, MODE, F, true, BLOCKS);                                                               \
+    else DL_LAUNCH2(T, R, MODE, F, false, BLOCKS);                                                                    \
+  } while (0)
+#define DL_LAUNCH2(T, R, MODE, F, A, BLOCKS)                                                                          \
+  do {                                                                                                                \
     if (smem > 48 * 1024)                                                                                             \
-      cudaFuncSetAttribute(dl::ssm_scan_kernel<T, R, MODE, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
-    dl::ssm_scan_kernel<T, R, MODE, F><<<dim3(BLOCKS, H, slices), threads, smem, stream>>>(                            \
+      cudaFuncSetAttribute(dl::ssm_scan_kernel<T, R, MODE, F, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    dl::ssm_scan_kernel<T, R, MODE, F, A><<<dim3(BLOCKS, H, slices), threads, smem, stream>>>(                         \
         static_cast<const T*>(u), u_stride, static_cast<const T*>(proj), proj_stride, dt_col, dt_bias, a_log, d_skip,  \
         state, static_cast<size_t>(state_stride), q_start, state_slots, segments, scratch, seg_decay, whole_up_to, y,  \
         H, P, N, G, PV, NS);                                                                                           \
@@ -382,6 +442,7 @@ DL_EXPORT int dl_ssm_scan(int dtype, const void* u, int u_stride, const void* pr
 #undef DL_MODE
 #undef DL_PICK
 #undef DL_LAUNCH
+#undef DL_LAUNCH2
   return dl::launch_status();
 }
 
