@@ -65,7 +65,10 @@ __global__ void ssm_conv_vec_kernel(const T* __restrict__ proj, int proj_stride,
   const float* kept = state + static_cast<size_t>(ck_request(row_slot[row])) * state_stride + keep_off;
   float acc[V];
 #pragma unroll
-  for (int j = 0; j < V; ++j) acc[j] = bias ? bias[ch + j] : 0.0f;
+  for (int j = 0; j < V; j += 4) {
+    const float4 b4 = bias ? *reinterpret_cast<const float4*>(bias + ch + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    acc[j] = b4.x; acc[j + 1] = b4.y; acc[j + 2] = b4.z; acc[j + 3] = b4.w;
+  }
   for (int k = K - 1; k >= 0; --k) {                               // oldest input first
     const int p = pos - k;
     float v[V];
@@ -74,11 +77,15 @@ __global__ void ssm_conv_vec_kernel(const T* __restrict__ proj, int proj_stride,
     } else {
       const float* kr = kept + static_cast<size_t>(K - 1 - (first - p)) * channels + ch;
 #pragma unroll
-      for (int j = 0; j < V; ++j) v[j] = kr[j];
+      for (int j = 0; j < V; ++j) v[j] = kr[j];          // (kept inputs begin where the state's layout puts them: no wide loads)
     }
     const float* tk = taps + static_cast<size_t>(K - 1 - k) * channels + ch;
 #pragma unroll
-    for (int j = 0; j < V; ++j) acc[j] = fmaf(tk[j], v[j], acc[j]);
+    for (int j = 0; j < V; j += 4) {
+      const float4 t4 = *reinterpret_cast<const float4*>(tk + j);
+      acc[j] = fmaf(t4.x, v[j], acc[j]); acc[j + 1] = fmaf(t4.y, v[j + 1], acc[j + 1]);
+      acc[j + 2] = fmaf(t4.z, v[j + 2], acc[j + 2]); acc[j + 3] = fmaf(t4.w, v[j + 3], acc[j + 3]);
+    }
   }
 #pragma unroll
   for (int j = 0; j < V; ++j) acc[j] = silu_f(acc[j]);
@@ -324,6 +331,59 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __
   }
 }
 
+// The same with 8 channels a thread held in registers (one pass over memory, 16-byte accesses): for parts of a multiple of
+// 8 channels, at most 8 * GN_CHUNKS * blockDim of them.
+constexpr int GN_CHUNKS = 4;
+template <typename T>
+__global__ void gated_group_norm_vec_kernel(const float* __restrict__ y, const T* __restrict__ z, int z_stride,
+                                            const float* __restrict__ w, float eps, T* __restrict__ out, int inner,
+                                            int part_len) {
+  __shared__ float red[33];
+  const int row = blockIdx.x, c0 = blockIdx.y * part_len;
+  const float* yr = y + static_cast<size_t>(row) * inner + c0;
+  const T* zr = z + static_cast<size_t>(row) * z_stride + c0;
+  float v[GN_CHUNKS][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < GN_CHUNKS; ++k) {
+    const int i = (k * blockDim.x + threadIdx.x) * 8;
+    if (i < part_len) {
+      const float4 a = *reinterpret_cast<const float4*>(yr + i), b = *reinterpret_cast<const float4*>(yr + i + 4);
+      float g[8];
+      if (sizeof(T) == 2) {
+        unpack<bf16>(*reinterpret_cast<const Vec16*>(zr + i), g);
+      } else {
+        unpack<float>(*reinterpret_cast<const Vec16*>(zr + i), g);
+        unpack<float>(*reinterpret_cast<const Vec16*>(zr + i + 4), g + 4);
+      }
+      const float yv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[k][j] = yv[j] * silu_f(g[j]);
+        ss = fmaf(v[k][j], v[k][j], ss);
+      }
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(part_len) + eps);
+  T* orow = out + static_cast<size_t>(row) * inner + c0;
+#pragma unroll
+  for (int k = 0; k < GN_CHUNKS; ++k) {
+    const int i = (k * blockDim.x + threadIdx.x) * 8;
+    if (i < part_len) {
+      const float4 wa = *reinterpret_cast<const float4*>(w + c0 + i), wb = *reinterpret_cast<const float4*>(w + c0 + i + 4);
+      float o[8] = {v[k][0] * inv * wa.x, v[k][1] * inv * wa.y, v[k][2] * inv * wa.z, v[k][3] * inv * wa.w,
+                    v[k][4] * inv * wb.x, v[k][5] * inv * wb.y, v[k][6] * inv * wb.z, v[k][7] * inv * wb.w};
+      if (sizeof(T) == 2) {
+        *reinterpret_cast<Vec16*>(orow + i) = pack<bf16>(o);
+      } else {
+        *reinterpret_cast<Vec16*>(orow + i) = pack<float>(o);
+        *reinterpret_cast<Vec16*>(orow + i + 4) = pack<float>(o + 4);
+      }
+    }
+  }
+}
+
 }  // namespace dl
 
 // out[row, ch] = silu(bias[ch] + sum_k taps[k, ch] * input(row's position - (K - 1 - k), ch)), the inputs being
@@ -339,7 +399,8 @@ DL_EXPORT int dl_ssm_conv(int dtype, const void* proj, int proj_stride, int col0
   if (dtype != 0 && dtype != 1) return DL_ERR_UNSUPPORTED;
   const int vec = dtype == 0 ? 4 : 8;
   const bool wide = channels % vec == 0 && col0 % vec == 0 && proj_stride % vec == 0 &&
-                    (reinterpret_cast<uintptr_t>(proj) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+                    (reinterpret_cast<uintptr_t>(proj) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(taps) & 15) == 0 && (bias == nullptr || (reinterpret_cast<uintptr_t>(bias) & 15) == 0);
   const size_t items = static_cast<size_t>(rows) * (wide ? channels / vec : channels);
   const unsigned blocks = static_cast<unsigned>((items + threads - 1) / threads);
 #define DL_LAUNCH(KERNEL, T)                                                                                         \
@@ -452,8 +513,21 @@ DL_EXPORT int dl_gated_group_norm(int dtype, const float* y, const void* z, int 
   if (rows <= 0) return 0;
   if (inner <= 0 || parts <= 0 || inner % parts != 0 || parts > 65535) return DL_ERR_UNSUPPORTED;
   const int part_len = inner / parts;
-  const int threads = part_len >= 1024 ? 256 : (part_len >= 256 ? 128 : 64);
   dim3 grid(rows, parts);
+  if ((dtype == 0 || dtype == 1) && part_len % 8 == 0 && part_len <= 8 * dl::GN_CHUNKS * 256 && inner % 8 == 0 && z_stride % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(y) & 15) == 0 && (reinterpret_cast<uintptr_t>(z) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    int vt = (part_len / 8 + 31) / 32 * 32;                         // a thread per 8 channels, whole warps, 256 at most
+    if (vt > 256) vt = 256;
+    if (dtype == 0)
+      dl::gated_group_norm_vec_kernel<float><<<grid, vt, 0, stream>>>(y, static_cast<const float*>(z), z_stride, w, eps,
+                                                                      static_cast<float*>(out), inner, part_len);
+    else
+      dl::gated_group_norm_vec_kernel<dl::bf16><<<grid, vt, 0, stream>>>(y, static_cast<const dl::bf16*>(z), z_stride, w, eps,
+                                                                         static_cast<dl::bf16*>(out), inner, part_len);
+    return dl::launch_status();
+  }
+  const int threads = part_len >= 1024 ? 256 : (part_len >= 256 ? 128 : 64);
   if (dtype == 0)
     dl::gated_group_norm_kernel<float><<<grid, threads, 0, stream>>>(y, static_cast<const float*>(z), z_stride, w, eps,
                                                                      static_cast<float*>(out), inner, part_len);

@@ -307,9 +307,9 @@ def test_long_portions_run_as_segments_side_by_side(dtype, H, P, N, G):
 def test_gate_comes_before_the_norm_of_every_part(dtype):
     from dynalm_b200.kernels import ops
     rng = np.random.RandomState(8)
-    for inner, parts, rows in ((128, 2, 5), (100, 1, 3), (96, 3, 4), (2048, 4, 2), (30, 5, 7)):
+    for inner, parts, rows in ((128, 2, 5), (100, 1, 3), (96, 3, 4), (2048, 4, 2), (30, 5, 7), (4096, 8, 3), (16384, 1, 2)):
         y = _t(rng.randn(rows, inner) * 3)
-        z = _t(rng.randn(rows, inner + 9) * 2, dtype)                           # the gate's columns first, others behind
+        z = _t(rng.randn(rows, inner + (9 if parts == 5 or inner == 128 else 8)) * 2, dtype)   # the gate's columns first, others behind
         w = _t(1 + 0.3 * rng.randn(inner))
         out = torch.zeros(rows, inner, dtype=dtype, device=DEV)
         ops.gated_group_norm(y, z, w, 1e-5, parts, out)
