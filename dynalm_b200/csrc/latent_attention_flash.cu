@@ -17,7 +17,7 @@
 // request was cut or what else the step holds. A unit at position p sees keys t with 0 <= p - t < window (window 0:
 // all t <= p); the sink of its head enters the denominator at the end. Exponentials are ex2.approx of scores scaled
 // by log2(e). R and r are run-time multiples of 8, R at most 512; every size comes with the launch.
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace dl {
 
@@ -70,6 +70,7 @@ struct LatentFlashParams {
   int out_stride;
   int H, R, r, page_size, window, HG;      // HG heads of QR = 32 / HG rows to a block (one row when HG = 32)
   float scale;
+  int* status;             // (bulk copies) receives LF_ERR_COPY when a wait for a tile's records gives up
   int parts;               // > 1: the key tiles of every query tile are dealt over this many blocks (blockIdx.z), which
   float* scratch;          // leave (max, sum, O) per unit in scratch [row, head, part, R + 2] for the merge kernel
 };
@@ -93,10 +94,48 @@ __device__ __forceinline__ void lf_load_keys(const LatentFlashParams& p, const i
   }
 }
 
-// NT: 8-column tiles of O per warp (R <= 64 NT).
-template <int NT>
+// The same with ONE bulk copy per record (cp.async.bulk, completion counted in bytes on the stage's mbarrier) instead of
+// 16-byte pieces: 64 copy instructions a tile instead of several thousand, issued by the first warp, each lane its keys
+// `lane` and `lane + 32`. Rows of keys outside [lo, hi] are zeroed by ordinary stores.
+__device__ __forceinline__ void lf_load_keys_bulk(const LatentFlashParams& p, const int* table, bf16* stage, int RS, int RW,
+                                                  int t0, int lo, int hi, int lane, uint64_t* bar) {
+  const uint32_t bytes = static_cast<uint32_t>(RW) * 2u;
+  const bf16* src[2];
+  bool valid[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int t = t0 + lane + 32 * i;
+    valid[i] = t >= lo && t <= hi;
+    src[i] = p.cache;
+    if (valid[i]) {
+      const int page = ck_page(table, t / p.page_size, p.max_blocks);
+      src[i] += (static_cast<size_t>(page) * p.page_size + t % p.page_size) * RW;
+    }
+  }
+  const int n_valid = __popc(__ballot_sync(0xffffffffu, valid[0])) + __popc(__ballot_sync(0xffffffffu, valid[1]));
+  // ordinary stores into this stage (zeroed rows of an earlier tile) come before the copies that write it now
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_valid) * bytes);      // (one arrival: the phase ends when the bytes are in)
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    bf16* dst = stage + static_cast<size_t>(lane + 32 * i) * RS;
+    if (valid[i]) {
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(smem_u32(dst)), "l"(src[i]), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+    } else {
+      for (int c = 0; c < RW; c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+}
+
+constexpr int LF_ERR_COPY = 31;    // status code: a tile's records did not arrive within about a second
+
+// NT: 8-column tiles of O per warp (R <= 64 NT). BULK: records by bulk copies and mbarriers instead of cp.async pieces.
+template <int NT, bool BULK>
 __global__ void __launch_bounds__(LF_THREADS, 1)
 latent_attention_flash_kernel(const LatentFlashParams p) {
+  __shared__ __align__(8) uint64_t lf_bar[2];
+  __shared__ int lf_abort;
   extern __shared__ __align__(16) unsigned char lf_smem[];
   const int RW = p.R + p.r;
   const int RWp = (RW + 15) & ~15;
@@ -107,6 +146,12 @@ latent_attention_flash_kernel(const LatentFlashParams p) {
   float* sPMax = reinterpret_cast<float*>(sP + LF_M * LF_PS);   // [4][32]
   float* sPSum = sPMax + 4 * LF_M;                          // [4][32]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, q4 = lane & 3;
+  if (BULK && tid == 0) {
+    mbar_init(&lf_bar[0], 1);
+    mbar_init(&lf_bar[1], 1);
+    lf_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
   pdl_wait();
   pdl_trigger();
   const int4 tile = ck_tile(reinterpret_cast<const int4*>(p.tiles)[blockIdx.x]);
@@ -114,6 +159,7 @@ latent_attention_flash_kernel(const LatentFlashParams p) {
   const int h0 = blockIdx.y * p.HG;
   const int heads = min(p.HG, p.H - h0);                    // heads of this block
   if (rows <= 0) return;
+  if (BULK) __syncthreads();                                 // the barriers are initialised
   const int* table = p.block_table + static_cast<size_t>(slot) * p.max_blocks;
   const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;       // the oldest key the first row sees
   const int hi = pos0 + rows - 1;                                       // the newest key the last row sees
@@ -141,8 +187,12 @@ latent_attention_flash_kernel(const LatentFlashParams p) {
     first_tile += static_cast<int>(blockIdx.z) * per;
     last_tile = min(last_tile, first_tile + per - 1);
   }
-  lf_load_keys(p, table, sK, RS, RW, first_tile * LF_KT, lo, hi, warp, lane);
-  lf_commit();
+  if (BULK) {
+    if (warp == 0) lf_load_keys_bulk(p, table, sK, RS, RW, first_tile * LF_KT, lo, hi, lane, &lf_bar[0]);
+  } else {
+    lf_load_keys(p, table, sK, RS, RW, first_tile * LF_KT, lo, hi, warp, lane);
+    lf_commit();
+  }
 
   // the four units whose output this thread holds: g, g + 8, 16 + g, 24 + g; their positions and validity
   int upos[4];
@@ -168,12 +218,21 @@ latent_attention_flash_kernel(const LatentFlashParams p) {
 
   for (int kt = first_tile; kt <= last_tile; ++kt) {
     bf16* stage = sK + static_cast<size_t>((kt - first_tile) & 1) * LF_KT * RS;
-    lf_wait<0>();
-    __syncthreads();                                        // the tile is here; everyone is done with the one before
-    if (kt < last_tile) {
-      lf_load_keys(p, table, sK + static_cast<size_t>((kt - first_tile + 1) & 1) * LF_KT * RS, RS, RW, (kt + 1) * LF_KT, lo, hi,
-                   warp, lane);
-      lf_commit();
+    if (BULK) {
+      const int ti = kt - first_tile;
+      const bool ok = mbar_wait(&lf_bar[ti & 1], (ti >> 1) & 1, p.status, LF_ERR_COPY, &lf_abort);
+      if (!__syncthreads_and(ok)) return;                   // (uniform: all leave, nothing is written)
+      if (kt < last_tile && warp == 0)
+        lf_load_keys_bulk(p, table, sK + static_cast<size_t>((ti + 1) & 1) * LF_KT * RS, RS, RW, (kt + 1) * LF_KT, lo, hi, lane,
+                          &lf_bar[(ti + 1) & 1]);
+    } else {
+      lf_wait<0>();
+      __syncthreads();                                      // the tile is here; everyone is done with the one before
+      if (kt < last_tile) {
+        lf_load_keys(p, table, sK + static_cast<size_t>((kt - first_tile + 1) & 1) * LF_KT * RS, RS, RW, (kt + 1) * LF_KT, lo, hi,
+                     warp, lane);
+        lf_commit();
+      }
     }
     // ---- scores of (units 16 mt .. +15) x (keys 16 kq .. +15) ------------------------------------------------
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -278,7 +337,11 @@ latent_attention_flash_kernel(const LatentFlashParams p) {
   }
   if (p.parts > 1) {
     // ---- a part: (max, sum, O) of every unit to scratch; the merge kernel finishes --------------------------------------
-    lf_wait<0>();                                            // (a part without key tiles has its one load in flight)
+    if (BULK) {                                              // (a part without key tiles has its one load in flight)
+      if (first_tile > last_tile) mbar_wait(&lf_bar[0], 0, p.status, LF_ERR_COPY, &lf_abort);
+    } else {
+      lf_wait<0>();
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       if (!uok[i]) continue;
@@ -367,8 +430,9 @@ static size_t lf_smem_bytes(int R, int r) {
 DL_EXPORT int dl_latent_attention_flash(const void* qw, int q_stride, const void* cache, const int* block_table, int max_blocks,
                                         const int* tiles, int n_tiles, const float* sink, void* out, int out_stride, int H, int R,
                                         int r, int page_size, float scale, int window, int HG, int parts, float* scratch,
-                                        int rows, cudaStream_t stream) {
+                                        int rows, int bulk, int* status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (bulk && status == nullptr) return DL_ERR_UNSUPPORTED;
   if (parts < 1 || parts > 64 || (parts > 1 && (scratch == nullptr || rows <= 0 || (reinterpret_cast<uintptr_t>(scratch) & 7) != 0)))
     return DL_ERR_UNSUPPORTED;
   if (H <= 0 || R <= 0 || R % 8 != 0 || r % 8 != 0 || r < 0 || R > 512 || page_size <= 0 || window < 0 || HG <= 0 || HG > 32 ||
@@ -390,23 +454,30 @@ DL_EXPORT int dl_latent_attention_flash(const void* qw, int q_stride, const void
   p.out_stride = out_stride;
   p.H = H; p.R = R; p.r = r; p.page_size = page_size; p.window = window; p.HG = HG;
   p.scale = scale;
+  p.status = status;
   p.parts = parts;
   p.scratch = scratch;
   const int groups = (H + HG - 1) / HG;
   if (groups > 65535) return DL_ERR_UNSUPPORTED;
   dim3 grid(n_tiles, groups, parts);
   int code;
-#define DL_LAUNCH(NT)                                                                                                    \
+#define DL_LAUNCH2(NT, B)                                                                                                \
   do {                                                                                                                   \
-    cudaError_t e = cudaFuncSetAttribute(dl::latent_attention_flash_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+    cudaError_t e = cudaFuncSetAttribute(dl::latent_attention_flash_kernel<NT, B>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                          static_cast<int>(smem));                                                        \
     if (e != cudaSuccess) return static_cast<int>(e);                                                                    \
-    code = dl::launch_streaming(dl::latent_attention_flash_kernel<NT>, grid, dim3(dl::LF_THREADS), smem, stream, p);      \
+    code = dl::launch_streaming(dl::latent_attention_flash_kernel<NT, B>, grid, dim3(dl::LF_THREADS), smem, stream, p);   \
+  } while (0)
+#define DL_LAUNCH(NT)            \
+  do {                           \
+    if (bulk) DL_LAUNCH2(NT, true); \
+    else DL_LAUNCH2(NT, false);  \
   } while (0)
   if (R <= 128) DL_LAUNCH(2);
   else if (R <= 256) DL_LAUNCH(4);
   else DL_LAUNCH(8);
 #undef DL_LAUNCH
+#undef DL_LAUNCH2
   if (code != 0 || parts == 1) return code;
   return dl::launch_streaming(dl::latent_merge_kernel, dim3(rows, H), dim3(128), 0, stream, static_cast<const float*>(scratch), sink,
                               static_cast<dl::bf16*>(out), out_stride, H, R, parts);

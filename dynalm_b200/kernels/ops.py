@@ -47,7 +47,8 @@ _SIGNATURES = {
     "head_linear_tc": {
         "dl_head_linear_tc": [_P, _I, _I, _I, _P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _P]},
     "latent_attention_flash": {
-        "dl_latent_attention_flash": [_P, _I, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _I, _P]},
+        "dl_latent_attention_flash": [_P, _I, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _I, _I, _P,
+                                      _P]},
     "qk_norm_cache": {
         "dl_qk_norm_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _L, _I, _I, _P, _P, _F, _F, _I, _I, _I, _I, _I, _I,
                                    _I, _I, _P]},
@@ -791,6 +792,11 @@ def latent_attention(qw: torch.Tensor, cache: torch.Tensor, block_table: torch.T
         _stream()), "latent_attention")
 
 
+# Records of the tensor-core latent attention by one bulk copy each (completion on an mbarrier) instead of 16-byte
+# cp.async pieces; DYNALM_LATENT_BULK=0 keeps the pieces.
+LATENT_BULK = os.environ.get("DYNALM_LATENT_BULK", "1") != "0"
+
+
 def latent_flash_fits(kv_rank: int, rot_dim: int) -> bool:
     """Whether the tensor-core latent attention's shared memory (32 query units and two tiles of 64 records) fits a block."""
     stride = ((kv_rank + rot_dim + 15) & ~15) + 8
@@ -827,7 +833,8 @@ def latent_attention_flash(qw: torch.Tensor, cache: torch.Tensor, block_table: t
     _check(_fn("latent_attention_flash", "dl_latent_attention_flash")(
         _p(qw), qw.stride(0), _p(cache), _p(block_table), block_table.stride(0), _p(tiles), n_tiles, _p(sink), _p(out),
         out.stride(0), heads, kv_rank, rot_dim, page_size, scale, window, heads_per_block, parts,
-        _p(scratch) if parts > 1 else None, rows, _stream()), "latent_attention_flash")
+        _p(scratch) if parts > 1 else None, rows, 1 if LATENT_BULK else 0, _p(_status_word(qw.device)), _stream()),
+        "latent_attention_flash")
     if parts > 1:
         global LAUNCHES
         LAUNCHES += 1
